@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200Q_VERSION 2
+#define B200Q_VERSION 3
 
 #define B200Q_OK 0
 #define B200Q_EINVAL (-1)   /* bad argument / unsupported shape            */
@@ -187,6 +187,83 @@ int b200q_gemm_geglu_bf16(const void* A_dev, const void* W_dev, void* C_dev,
  *     l <- bf16(bf16(tanh(bf16(l / cap))) * cap)               (vllm logits_processor.py:66-69) */
 int b200q_softcap_bf16(void* logits_dev, int64_t n, float cap, void* stream);
 
+/* ---- layered architectures (B200Q_ARCH_RAMOPEL): op-level entry points ---------------------------
+ * `dtype` (B200Q_DTYPE_*) is the element type of every `void*` matrix, activation and cache argument;
+ * `float*` arguments are fp32 in both modes.  What the design wants exact (residual sum, norms, scores
+ * and softmax, router, recurrent state and its gates) is fp32 in both; angles are fp64. */
+
+/* x[t,:] = table[ids[t],:] * scale into the fp32 residual; ids < 0 as in b200q_embed_ex */
+int b200q_embed_f32(const int32_t* ids_dev, const int32_t* prev_out_dev, const void* table_dev,
+                    float* out_dev, int T, int W, float scale, int dtype, void* stream);
+/* zero-centred RMS norm of fp32 rows, one or two weights at once (the two branches of a parallel
+ * layer): y_k = x / sqrt(mean(x^2) + eps) * (1 + w_k); y2/w2 may be NULL; rows != NULL gathers
+ * x[rows[i]] into y[i] */
+int b200q_centered_rmsnorm(const float* x_dev, const int32_t* rows_dev, const float* w1_dev,
+                           const float* w2_dev, void* y1_dev, void* y2_dev, int n, int W, float eps,
+                           int dtype, void* stream);
+/* C[m,n] = sum_k A[m,k] W[n,k] (+ bias[n]) for ANY M, N, K (fp32 accumulation in ascending k; true
+ * fp32 products for fp32 operands).  bf16 shapes the tcgen05 GEMM takes (K, N multiples of 64, dense
+ * rows, no bias, bf16 out) run on it.  out_f32: C is fp32 whatever dtype says. */
+int b200q_linear(const void* A_dev, int lda, const void* W_dev, const float* bias_dev, void* C_dev, int ldc,
+                 int M, int N, int K, int dtype, int out_f32, void* stream);
+/* the same per batch index b (per-head weights): A + b*a_bs, W + b*w_bs, C + b*c_bs (strides in elements) */
+int b200q_linear_batched(const void* A_dev, int lda, long long a_bs, const void* W_dev, long long w_bs,
+                         void* C_dev, int ldc, long long c_bs, int M, int N, int K, int batch, int dtype,
+                         int out_f32, void* stream);
+/* the same per group g (expert): rows [group_off[g], group_off[g+1]) of C use W + g*w_gs and read row
+ * a_rows[r] of A (a_rows NULL: row r); max_rows bounds a group's rows */
+int b200q_linear_grouped(const void* A_dev, int lda, const int32_t* a_rows_dev, const void* W_dev,
+                         long long w_gs, void* C_dev, int ldc, const int32_t* group_off_dev, int groups,
+                         int max_rows, int N, int K, int dtype, void* stream);
+/* latent attention 1/3: proj row = [query latent | kv latent | shared rotated key part];
+ *     cq = rmsnorm(query latent) * w_qn;  cache row slot_mapping[t] = [rmsnorm(kv latent) * w_kvn |
+ *     rotate(key part)], pairs (2i, 2i+1) of the first rot_dims entries turned by position * freq[i]
+ *     (freq: fp64 [rot_dims/2]).  has_kv = 0: query part only (the layer reads another layer's cache). */
+int b200q_latent_prep(const void* proj_dev, int ldp, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                      const double* freq_dev, const int32_t* positions_dev, const int32_t* slot_mapping_dev,
+                      const float* w_qn_dev, const float* w_kvn_dev, void* cq_dev, void* cache_dev,
+                      int has_kv, int T, float eps, int dtype, void* stream);
+/* latent attention 2/3: rotated query parts, turned, into qa[t, h, kv_rank:] (qa: fp32 [T, heads,
+ *     kv_rank + rot_dim]; its first kv_rank entries are W_uk[h]^T q_unrotated, written by a batched linear) */
+int b200q_rope_pairs_q(const void* q_dev, int heads, int dim, int rot_dim, int rot_dims, const double* freq_dev,
+                       const int32_t* positions_dev, float* qa_dev, int kv_rank, int T, int dtype, void* stream);
+/* latent attention 3/3: out[t,h,:] = softmax_j(scale * qa[t,h] . row_j) . latent_j over the keys
+ *     max(0, p - window + 1) <= j <= p of the token's sequence (window 0: all), rows read through the
+ *     block table (cache: [blocks][block_size][kv_rank + rot_dim]); out [T, heads, kv_rank] */
+int b200q_latent_attn(const float* qa_dev, const void* cache_dev, const int32_t* block_table_dev, int bt_stride,
+                      const int32_t* row_seq_dev, const int32_t* positions_dev, int T, int heads, int kv_rank,
+                      int rot_dim, int block_size, int window, float scale, void* out_dev, int dtype,
+                      void* stream);
+/* generalized delta rule over the sequences of a step (seq_desc as in b200q_batch); proj row =
+ *     [r | k | v | g | a | z] (heads*D each, z: Rk); state: fp32 [slots] x slot_stride, this layer's part
+ *     [heads][D][D] at the start of a slot.  Per token and head:
+ *     w = exp(-e^-1/2 sigmoid(w0 + W2 tanh z)), a = sigmoid(a + a_bias), u = k / sqrt(sum k^2 + 1e-6),
+ *     S <- diag(w) S - (a*u)(u^T S) + k v^T, o = S^T r, out = o / rms(o) * out_norm * sigmoid(g) */
+int b200q_delta_rule(const void* proj_dev, int ldp, const void* w2_dev, const float* w0_dev,
+                     const float* a_bias_dev, const float* out_norm_dev, float* state_dev, long long slot_stride,
+                     const int32_t* seq_desc_dev, int n_seqs, int heads, int D, int Rk, float eps, void* out_dev,
+                     int dtype, void* stream);
+/* PolyNorm over rows of F values: y = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3, N(v) = v / sqrt(mean(v^2) + eps) */
+int b200q_polynorm(const void* z_dev, const float* coef_dev, void* y_dev, int rows, int F, float eps, int dtype,
+                   void* stream);
+/* clamped gated unit: gate_up row = [g (F) | u (F)]; y = g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit),
+ *     u' = clamp(u, -limit, limit) */
+int b200q_clamped_glu(const void* gate_up_dev, void* y_dev, int64_t rows, int F, float limit, int dtype,
+                      void* stream);
+/* top-k routing over fp32 router logits [T, E]: idx/wts [T, top] (softmax over the chosen logits), and the
+ *     grouping of the T*top (token, choice) pairs by expert: group_off [E+1], perm_tok [T*top] (token of the
+ *     pair at each sorted position), pair_pos [T*top] (sorted position of pair t*top+k) */
+int b200q_moe_route(const float* logits_dev, int T, int E, int top, int32_t* idx_dev, float* wts_dev,
+                    int32_t* group_off_dev, int32_t* perm_tok_dev, int32_t* pair_pos_dev, void* stream);
+/* end of a parallel layer: x += mix + ff; ff = f (dense) or sum_k wts[t,k] expert_out[pair_pos[t*top+k]]
+ *     (+ sigmoid(shared_gate[t]) shared_out[t]); unused parts NULL */
+int b200q_layer_sum(float* x_dev, const void* mix_dev, const void* f_dev, const void* expert_out_dev,
+                    const int32_t* pair_pos_dev, const float* wts_dev, int top, const void* shared_out_dev,
+                    const float* shared_gate_dev, int T, int W, int dtype, void* stream);
+int b200q_argmax_f32(const float* logits_dev, int32_t* ids_dev, int B, int V, void* stream);
+int b200q_f32_to_bf16(const float* in_dev, void* out_dev, int64_t n, void* stream);
+int b200q_copy_f32(const float* in_dev, float* out_dev, int64_t n, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Model-level: one forward step over a mixed decode+prefill token batch.
  * Replaces GPUModelRunner.execute_model for LlamaForCausalLM
@@ -214,10 +291,50 @@ typedef struct b200q_model_config {
   float attn_softcap;     /* attention logit soft-capping (gemma2: 50); 0 = off                     */
   float final_softcap;    /* final logit soft-capping (gemma2: 30); 0 = off                         */
   float embed_scale;      /* embeddings are multiplied by this value (gemma2: bf16(sqrt(H))); 0 = off */
+  /* layered architectures (B200Q_ARCH_RAMOPEL); zero elsewhere */
+  int32_t dtype;          /* B200Q_DTYPE_BF16 | B200Q_DTYPE_F32: element type of matrices, activations, cache */
+  int32_t max_logit_rows; /* rows of the fp32 logits buffer (0 = max_seqs); a replayed step may ask for the
+                             logits of any of its rows                                                     */
+  int32_t state_slots;    /* recurrent-state slots (one per live sequence); 0 = max_seqs                    */
 } b200q_model_config;
 
 #define B200Q_ARCH_LLAMA 0
 #define B200Q_ARCH_GEMMA2 1
+/* Ramopel: a layered decoder.  Every layer is  x <- x + mixer(norm1 x) + ff(norm2 x)  with the residual
+ * x in fp32; the mixer and the feed-forward of each layer are chosen by its b200q_layer_desc. */
+#define B200Q_ARCH_RAMOPEL 2
+
+#define B200Q_DTYPE_BF16 0
+#define B200Q_DTYPE_F32 1
+
+#define B200Q_MIXER_LATENT_ATTN 1   /* low-rank (latent) queries and keys/values, sliding window, paged latent cache */
+#define B200Q_MIXER_GENERAL_DELTA 2 /* generalized delta-rule recurrence, fp32 state per (sequence, head)            */
+#define B200Q_FF_NONE 0
+#define B200Q_FF_POLYNORM 1         /* down(PolyNorm(up h))                                                          */
+#define B200Q_FF_MOE 2              /* top-k of clamped gated experts + an optional gated shared expert              */
+
+typedef struct b200q_layer_desc {
+  int32_t mixer;        /* B200Q_MIXER_*                                                               */
+  int32_t heads;
+  int32_t dim;          /* latent attention: unrotated q/k dims per head; delta: key = value dims       */
+  int32_t rot_dim;      /* latent attention: rotated q/k dims per head (one key part shared by heads)   */
+  int32_t vdim;         /* latent attention: value dims per head                                        */
+  int32_t q_rank;       /* latent attention: rows of the query down-projection                          */
+  int32_t kv_rank;      /* latent attention: size of the cached latent                                  */
+  int32_t kv_from;      /* latent attention: layer whose cached latents are read; -1 = its own          */
+  int32_t window;       /* keys seen: 0 <= i - j < window; 0 = all earlier keys                         */
+  int32_t rot_dims;     /* leading dims of the rotated part that are rotated (pairs 2i, 2i+1)           */
+  double rot_base;     /* pair i turns by position * rot_base^(-2i/rot_dims)                           */
+  float attn_scale;
+  int32_t decay_rank;   /* delta: inner size of the low-rank decay projection                           */
+  int32_t ff;           /* B200Q_FF_*                                                                   */
+  int32_t ff_dim;       /* dense: ff size; moe: ff size of one expert                                   */
+  int32_t n_experts;
+  int32_t top_k;
+  float expert_limit;
+  int32_t shared_dim;   /* moe: ff size of the shared expert, 0 = none                                  */
+  float shared_limit;
+} b200q_layer_desc;
 
 typedef struct b200q_model* b200q_model_t;
 
@@ -244,9 +361,47 @@ typedef struct b200q_batch {
   /* async stepping: token_ids[t] < 0 stands for prev_out_ids[-1 - token_ids[t]], a token the
    * previous step sampled and the host has not read back yet; NULL when no id is negative      */
   const int32_t* prev_out_ids;
+  /* per-sequence view of the same step (used by the layered architectures): row r of the block table is
+   * sequence r; seq_desc[r] = {first batch row, tokens this step, position of the first of them,
+   * recurrent-state slot}; row_seq[t] = sequence of batch row t.  NULL for callers that only run
+   * llama / gemma2 models. */
+  int32_t n_rows;
+  const int32_t* seq_desc;      /* [n_rows][4]                                                   */
+  const int32_t* row_seq;       /* [T]                                                           */
+  int32_t no_sampling;          /* 1: stop after the logits (sample_rows may then hold up to max_logit_rows rows) */
 } b200q_batch;
 
 int b200q_model_create(const b200q_model_config* cfg, b200q_model_t* out);
+/* B200Q_ARCH_RAMOPEL: cfg gives hidden (width), n_layers, vocab, block_size, max_tokens, max_seqs, max_pos,
+ * rms_eps, embed_scale, dtype; layers[n_layers] the mixer and feed-forward of every layer.
+ * Weights (b200q_model_bind_weight; matrices in cfg.dtype, row-major [out, in]; every vector and the
+ * PolyNorm constants in fp32 as one row):
+ *   "embed" [V, W], "final_norm" [1, W], "lm_head" [V, W]; per layer i, prefix "layers.i.":
+ *   "norm1", "norm2" [1, W]
+ *   latent attention: "mix.down" [q_rank (+ kv_rank + rot_dim if kv_from < 0), W] (query rows first),
+ *     "mix.q_norm" [1, q_rank], "mix.kv_norm" [1, kv_rank], "mix.uq" [heads*(dim+rot_dim), q_rank],
+ *     "mix.uk_t" [heads*kv_rank, dim] (each head's key up-projection TRANSPOSED: the query is carried into
+ *     the latent space, so scores are taken against the cached latent directly),
+ *     "mix.uv" [heads*vdim, kv_rank], "mix.o" [W, heads*vdim]
+ *   general delta: "mix.proj" [5*heads*dim + decay_rank, W] (rows: r, k, v, g, a, w1), "mix.w2"
+ *     [heads*dim, decay_rank], "mix.w0", "mix.a_bias", "mix.out_norm" [1, heads*dim], "mix.o" [W, heads*dim]
+ *   PolyNorm ff: "mlp.up" [ff, W], "mlp.act" [1, 4], "mlp.down" [W, ff]
+ *   MoE ff: "mlp.router" [E, W], "mlp.router_bias" [1, E], "mlp.experts_gate_up" [E*2*ff, W] (per expert:
+ *     gate rows then up rows), "mlp.experts_down" [E*W, ff], and with a shared expert
+ *     "mlp.shared_gate_up" [2*ffs, W], "mlp.shared_down" [W, ffs], "mlp.shared_gate" [1, W] */
+int b200q_model_create_layered(const b200q_model_config* cfg, const b200q_layer_desc* layers,
+                               b200q_model_t* out);
+/* layered models: bytes of one cache block over all layers that own a latent cache (the caller allocates
+ * num_blocks times this, zeroed, and binds it with b200q_model_bind_kv), and bytes of one recurrent-state
+ * slot over all recurrent layers (fp32; bound with b200q_model_bind_state) */
+int64_t b200q_model_kv_block_bytes(b200q_model_t m);
+int64_t b200q_model_state_slot_bytes(b200q_model_t m);
+int b200q_model_bind_state(b200q_model_t m, void* dev_ptr, int64_t n_slots);
+/* layered models: fp32 logits of the last forward, [n_sample, V] */
+const float* b200q_model_logits_f32_ptr(b200q_model_t m);
+/* layered models: copy the fp32 residual stream after every layer of the NEXT forwards into dev_ptr
+ * ([n_layers][T][W], the caller sizes it for the steps it runs); NULL switches it off */
+int b200q_model_set_layer_tap(b200q_model_t m, float* dev_ptr);
 int b200q_model_destroy(b200q_model_t m);
 /* names: "embed", "final_norm", "lm_head", and per layer i: "layers.i.input_norm",
  * "layers.i.qkv" [(n_q+2n_kv)D, H], "layers.i.o" [H, n_q D], "layers.i.post_norm",
@@ -262,6 +417,8 @@ int b200q_model_bind_kv(b200q_model_t m, void* dev_ptr, int64_t num_blocks);
 int b200q_model_bind_rope(b200q_model_t m, const void* dev_ptr);
 /* bytes needed for activations at cfg.max_tokens; caller allocates and binds */
 int64_t b200q_model_workspace_bytes(const b200q_model_config* cfg);
+/* the same for a created model of any architecture (a layered model's need depends on its layers) */
+int64_t b200q_model_workspace_bytes_of(b200q_model_t m);
 int b200q_model_bind_workspace(b200q_model_t m, void* dev_ptr, int64_t bytes);
 int b200q_model_forward(b200q_model_t m, const b200q_batch* batch, void* stream);
 /* debugging / parity: copy the bf16 logits of the last forward ([n_sample, V]) location */
@@ -356,6 +513,18 @@ int b200q_engine_has_work(b200q_engine_t e);
  * cap must be >= max_num_seqs. */
 int b200q_engine_step(b200q_engine_t e, int64_t* out_req_ids, int32_t* out_tokens,
                       int32_t* out_flags, int32_t cap, int32_t* n_out);
+/* Replay (teacher forcing): one step whose work the CALLER lays down instead of the scheduler — entry i
+ * appends n_tokens[i] given tokens to request req_ids[i] (admitted on its first entry: pages and a state
+ * slot are taken from the same pools the scheduler uses) and runs them through the same metadata
+ * builder, forward and kernels as a scheduled step, all entries as one batch.  want[] lists, per entry,
+ * the entry-relative token places whose logits are wanted; they are written, fp32, to logits_out
+ * [sum n_want][vocab] (host memory) in the order of the entries.  Nothing is sampled.  A request stays
+ * live (and may sit a step out) until b200q_engine_abort gives its pages and slot back.  Not to be mixed
+ * with b200q_engine_step on the same engine while requests are live.  B200Q_ENOMEM: the pool cannot hold
+ * the step. */
+int b200q_engine_step_replay(b200q_engine_t e, int32_t n_entries, const int64_t* req_ids,
+                             const int32_t* n_tokens, const int32_t* tokens, const int32_t* n_want,
+                             const int32_t* want, float* logits_out);
 int b200q_engine_get_stats(b200q_engine_t e, b200q_engine_stats* out);
 /* the engine's CUDA stream (cudaStream_t) so callers can record their own events on it */
 void* b200q_engine_stream(b200q_engine_t e);

@@ -34,6 +34,7 @@
 #include "common.cuh"
 
 namespace b200q {
+const float* model_logits_f32(b200q_model_t m);
 const b200q_model_config& model_cfg(b200q_model_t m);
 int64_t model_num_blocks(b200q_model_t m);
 bool model_is_profiling(b200q_model_t m);
@@ -61,6 +62,10 @@ struct Request {
   int32_t pending_slot = -1;
   int32_t refs = 0;             // in-flight steps that hold this request (0..2)
   bool dead = false;            // finished / aborted while a later step still holds it: no more events
+  int32_t state_slot = -1;      // recurrent-state slot, held while the request is in the running set
+  // replayed steps: entry-relative places whose logits are wanted this step, and where they go
+  std::vector<int32_t> want;
+  int64_t want_out = 0;
 };
 
 // one scheduled request of an in-flight step
@@ -93,6 +98,8 @@ struct b200q_engine {
   std::vector<Request*> running;
   std::vector<int32_t> free_blocks;
   int32_t total_blocks = 0;
+  // recurrent-state slots (one per running request; models without recurrent layers ignore them)
+  std::vector<int32_t> free_slots;
 
   // pinned host buffers are double-buffered (the host fills step k+1's while step k's H2D copy /
   // D2H read-back may still be pending); the device copies are single: everything is stream-ordered
@@ -154,6 +161,24 @@ static int expected_growth_blocks(const b200q_engine* e, const Request* r, int h
   return std::max(0, blocks - held);
 }
 
+// a request joins / leaves the running set: it holds a recurrent-state slot exactly while it is in it.
+// A slot given back may be handed out at once: the sequence that gets it starts at position 0, where the
+// recurrence starts from zero whatever the slot holds, and stream order protects a step in flight.
+static void enter_running(b200q_engine* e, Request* r) {
+  e->running.push_back(r);
+  if (r->state_slot < 0 && !e->free_slots.empty()) {
+    r->state_slot = e->free_slots.back();
+    e->free_slots.pop_back();
+  }
+}
+static void release_slot(b200q_engine* e, Request* r) {
+  if (r->state_slot >= 0) e->free_slots.push_back(r->state_slot);
+  r->state_slot = -1;
+}
+static void init_slots(b200q_engine* e) {
+  for (int32_t i = e->cfg.max_num_seqs - 1; i >= 0; --i) e->free_slots.push_back(i);
+}
+
 static bool ensure_blocks(b200q_engine* e, Request* r, int n_tokens_total) {
   const int need = (n_tokens_total + e->block_size - 1) / e->block_size;
   const int have = (int)r->blocks.size();
@@ -197,7 +222,8 @@ int b200q_engine_create(b200q_model_t model, const b200q_engine_config* cfg, b20
   // token_ids, positions, slot_mapping [T each]; ctx_lens [S]; sample_rows [S];
   // tiles [4 * (T/16 + S)]; block table [S * max_blocks_per_seq]
   e->meta_cap = 3 * T + 2 * S + 4 * S + 8 + 4 * (T / 16 + S + 2) +
-                S * (int64_t)((e->max_blocks_per_seq + 7) & ~7) + 64;
+                S * (int64_t)((e->max_blocks_per_seq + 7) & ~7) + 64 + /* seq_desc, row_seq, replay rows */ 4 * S + 2 * T + 16;
+  init_slots(e);
   cudaError_t ce;
   if ((ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking)) != cudaSuccess ||
       (ce = cudaMallocHost(&e->h_meta_buf[0], e->meta_cap * 4)) != cudaSuccess ||
@@ -248,7 +274,8 @@ int b200q_engine_create_dryrun(const b200q_engine_config* cfg, int32_t vocab, in
   for (int32_t b = num_blocks - 1; b >= 0; --b) e->free_blocks.push_back(b);
   const int64_t T = cfg->max_num_batched_tokens, S = cfg->max_num_seqs;
   e->meta_cap = 3 * T + 2 * S + 4 * S + 8 + 4 * (T / 16 + S + 2) +
-                S * (int64_t)((e->max_blocks_per_seq + 7) & ~7) + 64;
+                S * (int64_t)((e->max_blocks_per_seq + 7) & ~7) + 64 + /* seq_desc, row_seq, replay rows */ 4 * S + 2 * T + 16;
+  init_slots(e);
   for (int i = 0; i < 2; ++i) {
     e->h_meta_buf[i] = (int32_t*)malloc(e->meta_cap * 4);
     e->h_out_buf[i] = (int32_t*)malloc(S * 4);
@@ -352,6 +379,7 @@ static void retire_request(b200q_engine* e, Request* r) {
   auto ru = std::find(e->running.begin(), e->running.end(), r);
   if (ru != e->running.end()) e->running.erase(ru);
   free_request_blocks(e, r);
+  release_slot(e, r);
   auto it = e->by_id.find(r->id);
   if (it != e->by_id.end() && it->second == r) e->by_id.erase(it);
   if (r->refs == 0) delete r;
@@ -438,6 +466,8 @@ static int complete_step(b200q_engine* e, InFlightStep& st, int64_t* out_req_ids
   return B200Q_OK;
 }
 
+static int launch_step(b200q_engine* e, InFlightStep& step, std::vector<Request*>& sched, float* replay_out);
+
 // ---- scheduling + launch of the next step; `step.active` stays false when there is nothing to run
 static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
   int budget = e->cfg.max_num_batched_tokens;
@@ -477,6 +507,7 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
           sched.erase(sit);
         }
         free_request_blocks(e, victim);
+        release_slot(e, victim);
         victim->n_computed = 0;
         victim->n_sched = 0;
         e->waiting.push_front(victim);
@@ -528,7 +559,7 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
       if (!ensure_blocks(e, r, r->n_computed + n_new)) break;
       growth += r_growth;
       e->waiting.pop_front();
-      e->running.push_back(r);
+      enter_running(e, r);
       r->n_sched = n_new;
       budget -= n_new;
       sched.push_back(r);
@@ -557,7 +588,14 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
 
 
   if (sched.empty()) return B200Q_OK;
+  return launch_step(e, step, sched, nullptr);
+}
 
+// ---- metadata, launch and bookkeeping of one step over `sched` (every request with n_sched new tokens,
+// blocks in place).  replay_out != NULL: a replayed step — the logits of every request's `want` places
+// go to replay_out (host) and nothing is sampled.
+static int launch_step(b200q_engine* e, InFlightStep& step, std::vector<Request*>& sched, float* replay_out) {
+  const bool replay = replay_out != nullptr || (e->dry_run && !sched.empty() && !sched[0]->want.empty());
   // ---- 3. order: single-token pieces (decode) first, then multi-token prefill chunks ----
   std::stable_partition(sched.begin(), sched.end(), [](Request* r) { return r->n_sched == 1; });
   int n_dec = 0, T = 0, max_blocks = 1;
@@ -576,7 +614,9 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
   int32_t* slot = pos + T;
   int32_t* ctx = slot + T;
   int32_t* srows = ctx + n_dec;
-  int32_t* sparams = srows + n_rows;  // reserve n_rows sample slots
+  int n_want = 0;
+  for (Request* r : sched) n_want += (int)r->want.size();
+  int32_t* sparams = srows + std::max(n_rows, n_want);  // reserve the sample slots
   sparams += (4 - ((sparams - h_meta) & 3)) & 3;
   int32_t* tiles = sparams + 4 * n_rows;  // 16-byte aligned: the prefill kernel reads tiles as int4
   int n_tiles = 0, n_sample = 0, row = 0;
@@ -584,7 +624,9 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
   // count tiles first to place the block table after them
   for (Request* r : sched)
     if (r->n_sched > 1) n_tiles += (r->n_sched + 15) / 16;
-  int32_t* btab = tiles + 4 * n_tiles;
+  int32_t* sdesc = tiles + 4 * n_tiles;   // [n_rows][4] per-sequence view (16-byte aligned like tiles)
+  int32_t* rseq = sdesc + 4 * n_rows;     // [T] sequence of every batch row
+  int32_t* btab = rseq + T;
   // keep the block table 16-byte aligned for tidy copies
   btab += (4 - ((btab - h_meta) & 3)) & 3;
   const int64_t used = (btab - h_meta) + (int64_t)n_rows * bt_stride;
@@ -605,7 +647,12 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
       tok[row + j] = p == r->pending_pos ? -1 - r->pending_slot : r->tokens[p];
       pos[row + j] = p;
       slot[row + j] = r->blocks[p / bs] * bs + (p % bs);
+      rseq[row + j] = ri;
     }
+    sdesc[4 * ri + 0] = row;
+    sdesc[4 * ri + 1] = r->n_sched;
+    sdesc[4 * ri + 2] = r->n_computed;
+    sdesc[4 * ri + 3] = std::max(r->state_slot, 0);
     if (r->n_sched == 1) {
       ctx[ri] = r->n_computed + 1;
     } else {
@@ -617,7 +664,9 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
         ++ti;
       }
     }
-    if (r->n_computed + r->n_sched == (int)r->tokens.size()) {
+    if (replay) {
+      for (int32_t wpos : r->want) srows[n_sample++] = row + wpos;
+    } else if (r->n_computed + r->n_sched == (int)r->tokens.size()) {
       slot_of[ri] = n_sample;
       float tf = r->temperature;
       int32_t tbits;
@@ -645,6 +694,15 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
     };
     if (T > e->cfg.max_num_batched_tokens) fail("token budget exceeded");
     if (n_rows > e->cfg.max_num_seqs) fail("more sequences than max_num_seqs");
+    {
+      std::vector<char> slot_used((size_t)e->cfg.max_num_seqs, 0);
+      for (Request* r : sched)
+        if (r->state_slot < 0 || r->state_slot >= e->cfg.max_num_seqs || slot_used[r->state_slot]++)
+          fail("two sequences of one step share a recurrent-state slot");
+      for (int ri = 0; ri < n_rows; ++ri)
+        if (sdesc[4 * ri + 1] < 1 || pos[sdesc[4 * ri]] != sdesc[4 * ri + 2] || rseq[sdesc[4 * ri]] != ri)
+          fail("bad per-sequence descriptor");
+    }
     std::vector<char> slot_seen((size_t)e->total_blocks * e->block_size, 0);
     for (int t = 0; t < T && rc == B200Q_OK; ++t) {
       if (slot[t] < 0 || slot[t] >= (int)slot_seen.size()) fail("slot out of range");
@@ -686,6 +744,10 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
     b.out_ids = e->d_out;
     b.prev_out_ids = e->d_out;  // the in-flight step's ids: read by this step's embedding before its sampler overwrites them
     b.sample_params = any_sampled ? e->d_meta + (sparams - h_meta) : nullptr;
+    b.n_rows = n_rows;
+    b.seq_desc = e->d_meta + (sdesc - h_meta);
+    b.row_seq = e->d_meta + (rseq - h_meta);
+    b.no_sampling = replay ? 1 : 0;
     b.sum_ctx_dec = 0;
     b.prefill_flops_per_layer = 0;
     for (Request* r : sched) {
@@ -701,7 +763,7 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
     }
     int rc = B200Q_OK;
     bool launched = false;
-    if (e->use_graphs && n_tiles == 0 && T == n_dec && T < (1 << 21) && bt_stride < (1 << 20) &&
+    if (e->use_graphs && !replay && n_tiles == 0 && T == n_dec && T < (1 << 21) && bt_stride < (1 << 20) &&
         !model_is_profiling(e->model) &&
         e->stats.steps >= 2 /* first steps run eagerly: one-time attribute/occupancy/scratch setup */) {
       if (e->graph_epoch != tuning_epoch()) {  // a tuning hook changed kernel selection: rebuild
@@ -754,7 +816,21 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
     }
     if (!launched) rc = b200q_model_forward(e->model, &b, e->stream);
     if (rc) return rc;
-    if (n_sample > 0) {
+    if (replay) {
+      // the wanted logits, request by request, to the caller's order (want_out = first row there)
+      const float* lg = model_logits_f32(e->model);
+      const size_t V = (size_t)e->mcfg.vocab;
+      int64_t at = 0;
+      for (Request* r : sched) {
+        const size_t nw = r->want.size();
+        if (nw && (!lg || cudaMemcpyAsync(replay_out + (size_t)r->want_out * V, lg + (size_t)at * V, nw * V * 4,
+                                          cudaMemcpyDeviceToHost, e->stream) != cudaSuccess)) {
+          set_error("replay: this model keeps no fp32 logits, or the D2H copy failed");
+          return B200Q_ECUDA;
+        }
+        at += (int64_t)nw;
+      }
+    } else if (n_sample > 0) {
       ce = cudaMemcpyAsync(e->h_out_buf[buf], e->d_out, (size_t)n_sample * 4, cudaMemcpyDeviceToHost, e->stream);
       if (ce != cudaSuccess) {
         set_error("step: D2H copy failed: %s", cudaGetErrorString(ce));
@@ -808,8 +884,105 @@ static int schedule_and_launch(b200q_engine* e, InFlightStep& step) {
       auto ru = std::find(e->running.begin(), e->running.end(), se.r);
       if (ru != e->running.end()) e->running.erase(ru);
       free_request_blocks(e, se.r);
+      release_slot(e, se.r);
     }
   return B200Q_OK;
+}
+
+int b200q_engine_step_replay(b200q_engine_t e, int32_t n_entries, const int64_t* req_ids, const int32_t* n_tokens,
+                             const int32_t* tokens, const int32_t* n_want, const int32_t* want, float* logits_out) {
+  B200Q_CHECK_ARG(e && n_entries > 0 && req_ids && n_tokens && tokens && n_want && (want || true),
+                  "step_replay: bad argument");
+  B200Q_CHECK_ARG(e->dry_run || logits_out, "step_replay: logits_out is null");
+  if (e->inflight.active) {
+    set_error("step_replay: a scheduled step is in flight");
+    return B200Q_ESTATE;
+  }
+  B200Q_CHECK_ARG(n_entries <= e->cfg.max_num_seqs, "step_replay: %d entries exceed max_num_seqs=%d", n_entries,
+                  e->cfg.max_num_seqs);
+  // validate everything before any state changes
+  int64_t total = 0, total_want = 0;
+  {
+    int64_t to = 0, wo = 0;
+    for (int i = 0; i < n_entries; ++i) {
+      B200Q_CHECK_ARG(n_tokens[i] >= 1 && n_want[i] >= 0, "step_replay: entry %d has no tokens", i);
+      for (int j = 0; j < i; ++j) B200Q_CHECK_ARG(req_ids[j] != req_ids[i], "step_replay: request listed twice");
+      for (int j = 0; j < n_tokens[i]; ++j)
+        B200Q_CHECK_ARG(tokens[to + j] >= 0 && tokens[to + j] < e->mcfg.vocab, "step_replay: token id out of range");
+      for (int j = 0; j < n_want[i]; ++j)
+        B200Q_CHECK_ARG(want[wo + j] >= 0 && want[wo + j] < n_tokens[i], "step_replay: wanted place out of range");
+      auto it = e->by_id.find(req_ids[i]);
+      const int have = it == e->by_id.end() ? 0 : (int)it->second->tokens.size();
+      B200Q_CHECK_ARG(have + n_tokens[i] <= e->cfg.max_model_len, "step_replay: request exceeds max_model_len=%d",
+                      e->cfg.max_model_len);
+      to += n_tokens[i];
+      wo += n_want[i];
+    }
+    total = to;
+    total_want = wo;
+  }
+  B200Q_CHECK_ARG(total <= e->cfg.max_num_batched_tokens, "step_replay: %lld tokens exceed the step budget %d",
+                  (long long)total, e->cfg.max_num_batched_tokens);
+  if (!e->dry_run) {
+    const int cap = std::max(e->mcfg.max_logit_rows, e->mcfg.max_seqs);
+    B200Q_CHECK_ARG(total_want <= cap, "step_replay: %lld wanted rows exceed the logits buffer (%d)",
+                    (long long)total_want, cap);
+  }
+  int new_reqs = 0;
+  for (int i = 0; i < n_entries; ++i) new_reqs += e->by_id.find(req_ids[i]) == e->by_id.end();
+  if ((int)e->running.size() + new_reqs > e->cfg.max_num_seqs) {
+    set_error("step_replay: more than max_num_seqs=%d live requests", e->cfg.max_num_seqs);
+    return B200Q_ENOMEM;
+  }
+  std::vector<Request*> sched;
+  int64_t to = 0, wo = 0;
+  for (int i = 0; i < n_entries; ++i) {
+    Request* r;
+    auto it = e->by_id.find(req_ids[i]);
+    if (it == e->by_id.end()) {
+      r = new Request();
+      r->id = req_ids[i];
+      r->n_prompt = 0;
+      r->max_new = 0x3fffffff;
+      r->ignore_eos = true;
+      e->by_id[r->id] = r;
+      enter_running(e, r);
+    } else {
+      r = it->second;
+    }
+    r->tokens.insert(r->tokens.end(), tokens + to, tokens + to + n_tokens[i]);
+    r->n_prompt = (int32_t)r->tokens.size();
+    r->n_sched = n_tokens[i];
+    r->want.assign(want + wo, want + wo + n_want[i]);
+    r->want_out = wo;
+    to += n_tokens[i];
+    wo += n_want[i];
+    sched.push_back(r);
+  }
+  int rc = B200Q_OK;
+  for (Request* r : sched)
+    if (!ensure_blocks(e, r, r->n_computed + r->n_sched)) {
+      set_error("step_replay: the cache pool cannot hold this step (%d of %d blocks free)", (int)e->free_blocks.size(),
+                e->total_blocks);
+      rc = B200Q_ENOMEM;
+      break;
+    }
+  InFlightStep st;
+  if (!rc) rc = launch_step(e, st, sched, logits_out);
+  if (!rc && !e->dry_run && cudaStreamSynchronize(e->stream) != cudaSuccess) {
+    set_error("step_replay: forward failed: %s", cudaGetErrorString(cudaGetLastError()));
+    rc = B200Q_ECUDA;
+  }
+  for (StepEntry& se : st.entries) se.r->refs--;
+  for (Request* r : sched) {
+    r->want.clear();
+    if (rc) {  // the step did not run: its tokens are not part of the request
+      r->tokens.resize(r->tokens.size() - r->n_sched);
+      r->n_prompt = (int32_t)r->tokens.size();
+      r->n_sched = 0;
+    }
+  }
+  return rc;
 }
 
 int b200q_engine_step(b200q_engine_t e, int64_t* out_req_ids, int32_t* out_tokens,

@@ -1,0 +1,479 @@
+// layered.cu — model-level code of the layered architectures (B200Q_ARCH_RAMOPEL): creation from a list
+// of b200q_layer_desc, weight binding by name, cache / state / workspace layout, and one forward step over
+// a mixed batch (single decoded tokens beside portions of prompts), composed from the kernels of
+// layered_ops.cu.  The step's metadata is the engine's own (b200q_batch): block table, slot mapping,
+// positions, per-sequence descriptors.
+//
+// Layout.  Latent cache: one region per layer that owns latents, [num_blocks][block_size][kv_rank +
+// rot_dim] in the model's dtype — a layer with kv_from reads the region of the layer it names.  Recurrent
+// state: fp32 [slots][sum over delta layers of heads*dim*dim]; a slot belongs to one live sequence.
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+
+#include "model_types.cuh"
+
+using namespace b200q;
+
+namespace {
+
+int64_t al256(int64_t v) { return (v + 255) & ~(int64_t)255; }
+int esize(const b200q_model_config& c) { return c.dtype == B200Q_DTYPE_F32 ? 4 : 2; }
+int logit_rows(const b200q_model_config& c) { return std::max(c.max_logit_rows, c.max_seqs); }
+
+int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
+  B200Q_CHECK_ARG(c && L, "layered config is null");
+  B200Q_CHECK_ARG(c->arch == B200Q_ARCH_RAMOPEL, "create_layered: arch=%d is not a layered architecture", c->arch);
+  B200Q_CHECK_ARG(c->dtype == B200Q_DTYPE_BF16 || c->dtype == B200Q_DTYPE_F32, "dtype=%d unknown", c->dtype);
+  B200Q_CHECK_ARG(c->hidden > 0 && c->vocab > 0 && c->n_layers > 0 && c->max_tokens > 0 && c->max_seqs > 0 &&
+                      c->max_pos > 0 && c->block_size > 0 && c->rms_eps > 0.f,
+                  "bad sizes width=%d vocab=%d L=%d max_tokens=%d max_seqs=%d max_pos=%d block=%d", c->hidden,
+                  c->vocab, c->n_layers, c->max_tokens, c->max_seqs, c->max_pos, c->block_size);
+  for (int i = 0; i < c->n_layers; ++i) {
+    const b200q_layer_desc& d = L[i];
+    if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
+      B200Q_CHECK_ARG(d.heads > 0 && d.dim >= 0 && d.rot_dim >= 0 && d.dim + d.rot_dim > 0 && d.vdim > 0 &&
+                          d.q_rank > 0 && d.kv_rank > 0 && d.kv_rank <= 512 && d.window >= 0 && d.rot_dims >= 0 &&
+                          d.rot_dims % 2 == 0 && d.rot_dims <= d.rot_dim,
+                      "layer %d: bad latent attention sizes (kv_rank <= 512, even rot.dims <= rot_dim)", i);
+      if (d.kv_from >= 0) {
+        B200Q_CHECK_ARG(d.kv_from < i && L[d.kv_from].mixer == B200Q_MIXER_LATENT_ATTN && L[d.kv_from].kv_from < 0 &&
+                            L[d.kv_from].kv_rank == d.kv_rank && L[d.kv_from].rot_dim == d.rot_dim,
+                        "layer %d: kv_from=%d must name an earlier latent-attention layer with its own latents "
+                        "of the same sizes", i, d.kv_from);
+      }
+    } else if (d.mixer == B200Q_MIXER_GENERAL_DELTA) {
+      B200Q_CHECK_ARG(d.heads > 0 && d.dim > 0 && d.dim <= 1024 && d.decay_rank > 0,
+                      "layer %d: bad delta-rule sizes", i);
+    } else {
+      set_error("layer %d: unknown mixer %d", i, d.mixer);
+      return B200Q_EINVAL;
+    }
+    if (d.ff == B200Q_FF_POLYNORM) {
+      B200Q_CHECK_ARG(d.ff_dim > 0, "layer %d: bad ff size", i);
+    } else if (d.ff == B200Q_FF_MOE) {
+      B200Q_CHECK_ARG(d.ff_dim > 0 && d.n_experts > 0 && d.n_experts <= 4096 && d.top_k > 0 && d.top_k <= 32 &&
+                          d.top_k <= d.n_experts && d.shared_dim >= 0,
+                      "layer %d: bad mixture sizes (experts <= 4096, top <= 32)", i);
+    } else {
+      B200Q_CHECK_ARG(d.ff == B200Q_FF_NONE, "layer %d: unknown feed-forward %d", i, d.ff);
+    }
+  }
+  return B200Q_OK;
+}
+
+// widest use of every workspace buffer over the layers
+struct Widths {
+  int64_t proj = 1, cq = 1, q = 1, qa = 1, olat = 1, attn = 1, ffh = 1, ffa = 1, experts = 1, pairs = 1, egu = 1,
+          eact = 1;
+  bool moe = false, shared = false;
+};
+Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_layer>& Ls) {
+  Widths w;
+  for (const auto& l : Ls) {
+    const b200q_layer_desc& d = l.d;
+    if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
+      const int64_t RP = d.kv_rank + d.rot_dim;
+      w.proj = std::max<int64_t>(w.proj, d.q_rank + (d.kv_from < 0 ? RP : 0));
+      w.cq = std::max<int64_t>(w.cq, d.q_rank);
+      w.q = std::max<int64_t>(w.q, (int64_t)d.heads * (d.dim + d.rot_dim));
+      w.qa = std::max<int64_t>(w.qa, (int64_t)d.heads * RP);
+      w.olat = std::max<int64_t>(w.olat, (int64_t)d.heads * d.kv_rank);
+      w.attn = std::max<int64_t>(w.attn, (int64_t)d.heads * d.vdim);
+    } else {
+      w.proj = std::max<int64_t>(w.proj, 5 * (int64_t)d.heads * d.dim + d.decay_rank);
+      w.attn = std::max<int64_t>(w.attn, (int64_t)d.heads * d.dim);
+    }
+    if (d.ff == B200Q_FF_POLYNORM) {
+      w.ffh = std::max<int64_t>(w.ffh, d.ff_dim);
+      w.ffa = std::max<int64_t>(w.ffa, d.ff_dim);
+    } else if (d.ff == B200Q_FF_MOE) {
+      w.moe = true;
+      w.experts = std::max<int64_t>(w.experts, d.n_experts);
+      w.pairs = std::max<int64_t>(w.pairs, d.top_k);
+      w.egu = std::max<int64_t>(w.egu, (int64_t)d.top_k * 2 * d.ff_dim);
+      w.eact = std::max<int64_t>(w.eact, (int64_t)d.top_k * d.ff_dim);
+      if (d.shared_dim > 0) {
+        w.shared = true;
+        w.ffh = std::max<int64_t>(w.ffh, 2 * (int64_t)d.shared_dim);
+        w.ffa = std::max<int64_t>(w.ffa, d.shared_dim);
+      }
+    }
+  }
+  return w;
+}
+
+// one pass lays the workspace out; with base == nullptr it only measures
+int64_t layout(b200q_model* m, uint8_t* base) {
+  const b200q_model_config& c = m->cfg;
+  b200q_layered* y = m->lay;
+  const Widths w = widths_of(c, y->layers);
+  const int64_t T = c.max_tokens, W = c.hidden, es = esize(c), LR = logit_rows(c);
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) -> void* {
+    void* r = base ? base + off : nullptr;
+    off += al256(bytes);
+    return r;
+  };
+  y->x = (float*)take(T * W * 4);
+  y->h1 = take(T * W * es);
+  y->h2 = take(T * W * es);
+  y->mix = take(T * W * es);
+  y->ffo = take(T * W * es);
+  y->proj = take(T * w.proj * es);
+  y->cq = take(T * w.cq * es);
+  y->q = take(T * w.q * es);
+  y->qa = (float*)take(T * w.qa * 4);
+  y->olat = take(T * w.olat * es);
+  y->attn = take(T * w.attn * es);
+  y->ffh = take(T * w.ffh * es);
+  y->ffa = take(T * w.ffa * es);
+  y->rlog = (float*)take(T * w.experts * 4);
+  y->idx = (int32_t*)take(T * w.pairs * 4);
+  y->wts = (float*)take(T * w.pairs * 4);
+  y->perm_tok = (int32_t*)take(T * w.pairs * 4);
+  y->pair_pos = (int32_t*)take(T * w.pairs * 4);
+  y->group_off = (int32_t*)take((w.experts + 1) * 4);
+  y->egu = take(T * w.egu * es);
+  y->eact = take(T * w.eact * es);
+  y->eout = take(w.moe ? T * w.pairs * W * es : 1);
+  y->shout = take(w.shared ? T * W * es : 1);
+  y->sgate = (float*)take(T * 4);
+  y->sel = take(LR * W * es);
+  y->logits = (float*)take(LR * (int64_t)c.vocab * 4);
+  y->logits_bf16 = take((int64_t)c.max_seqs * c.vocab * 2);
+  return off;
+}
+
+}  // namespace
+
+namespace b200q {
+
+int layered_create(const b200q_model_config* cfg, const b200q_layer_desc* layers, b200q_model_t* out) {
+  B200Q_CHECK_ARG(out != nullptr, "out is null");
+  int rc = check_layered(cfg, layers);
+  if (rc) return rc;
+  rc = b200q_device_check();
+  if (rc) return rc;
+  b200q_model* m = new b200q_model();
+  m->cfg = *cfg;
+  m->lay = new b200q_layered();
+  m->lay->layers.resize(cfg->n_layers);
+  const int es = esize(*cfg);
+  for (int i = 0; i < cfg->n_layers; ++i) {
+    b200q_layered_layer& l = m->lay->layers[i];
+    l.d = layers[i];
+    if (l.d.mixer == B200Q_MIXER_LATENT_ATTN) {
+      if (l.d.kv_from < 0) {
+        l.cache_block_off = m->lay->kv_block_bytes;
+        m->lay->kv_block_bytes += (int64_t)cfg->block_size * (l.d.kv_rank + l.d.rot_dim) * es;
+      } else {
+        l.cache_block_off = m->lay->layers[l.d.kv_from].cache_block_off;
+      }
+      // rotation frequencies base^(-2i/dims), fp64
+      const int half = l.d.rot_dims / 2;
+      if (half > 0) {
+        std::vector<double> f(half);
+        for (int k = 0; k < half; ++k) f[k] = pow((double)l.d.rot_base, -2.0 * k / (double)l.d.rot_dims);
+        if (cudaMalloc(&l.freq, half * sizeof(double)) != cudaSuccess ||
+            cudaMemcpy(l.freq, f.data(), half * sizeof(double), cudaMemcpyHostToDevice) != cudaSuccess) {
+          set_error("create_layered: CUDA allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+          b200q_model_destroy(m);
+          return B200Q_ECUDA;
+        }
+      }
+    } else {
+      l.state_off = m->lay->state_slot_floats;
+      m->lay->state_slot_floats += (int64_t)l.d.heads * l.d.dim * l.d.dim;
+    }
+  }
+  *out = m;
+  return B200Q_OK;
+}
+
+void layered_destroy(b200q_model* m) {
+  if (!m->lay) return;
+  for (auto& l : m->lay->layers)
+    if (l.freq) cudaFree(l.freq);
+  delete m->lay;
+  m->lay = nullptr;
+}
+
+int64_t layered_workspace_bytes(b200q_model* m) { return layout(m, nullptr); }
+
+int layered_bind_workspace(b200q_model* m, void* p, int64_t bytes) {
+  const int64_t need = layout(m, nullptr);
+  B200Q_CHECK_ARG(bytes >= need, "workspace too small: %lld < %lld", (long long)bytes, (long long)need);
+  B200Q_CHECK_ARG((reinterpret_cast<uintptr_t>(p) & 255) == 0, "workspace must be 256-byte aligned");
+  m->ws = (uint8_t*)p;
+  m->ws_bytes = bytes;
+  layout(m, (uint8_t*)p);
+  return B200Q_OK;
+}
+
+int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t rows, int64_t cols) {
+  const b200q_model_config& c = m->cfg;
+  const int64_t W = c.hidden;
+  auto expect = [&](int64_t r, int64_t cc) -> int {
+    B200Q_CHECK_ARG(rows == r && cols == cc, "weight %s has shape [%lld,%lld], expected [%lld,%lld]", name,
+                    (long long)rows, (long long)cols, (long long)r, (long long)cc);
+    return B200Q_OK;
+  };
+  int rc;
+  if (!strcmp(name, "embed")) { if ((rc = expect(c.vocab, W))) return rc; m->embed = p; return B200Q_OK; }
+  if (!strcmp(name, "final_norm")) { if ((rc = expect(1, W))) return rc; m->final_norm = p; return B200Q_OK; }
+  if (!strcmp(name, "lm_head")) { if ((rc = expect(c.vocab, W))) return rc; m->lm_head = p; return B200Q_OK; }
+  int li = -1;
+  char field[48] = {0};
+  if (sscanf(name, "layers.%d.%47s", &li, field) != 2 || li < 0 || li >= c.n_layers) {
+    set_error("bind_weight: unknown weight name '%s'", name);
+    return B200Q_EINVAL;
+  }
+  b200q_layered_layer& l = m->lay->layers[li];
+  const b200q_layer_desc& d = l.d;
+  const int64_t HD = (int64_t)d.heads * d.dim;
+#define FIELD(fname, slot, r, cc)                        \
+  if (!strcmp(field, fname)) {                           \
+    if ((rc = expect((r), (cc)))) return rc;             \
+    *(const void**)&(slot) = p;                          \
+    return B200Q_OK;                                     \
+  }
+  FIELD("norm1", l.norm1, 1, W)
+  if (d.ff != B200Q_FF_NONE) FIELD("norm2", l.norm2, 1, W)
+  if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
+    const int64_t RP = d.kv_rank + d.rot_dim;
+    FIELD("mix.down", l.down, d.q_rank + (d.kv_from < 0 ? RP : 0), W)
+    FIELD("mix.q_norm", l.q_norm, 1, d.q_rank)
+    if (d.kv_from < 0) FIELD("mix.kv_norm", l.kv_norm, 1, d.kv_rank)
+    FIELD("mix.uq", l.uq, (int64_t)d.heads * (d.dim + d.rot_dim), d.q_rank)
+    FIELD("mix.uk_t", l.uk_t, (int64_t)d.heads * d.kv_rank, d.dim)
+    FIELD("mix.uv", l.uv, (int64_t)d.heads * d.vdim, d.kv_rank)
+    FIELD("mix.o", l.o, W, (int64_t)d.heads * d.vdim)
+  } else {
+    FIELD("mix.proj", l.proj, 5 * HD + d.decay_rank, W)
+    FIELD("mix.w2", l.w2, HD, d.decay_rank)
+    FIELD("mix.w0", l.w0, 1, HD)
+    FIELD("mix.a_bias", l.a_bias, 1, HD)
+    FIELD("mix.out_norm", l.out_norm, 1, HD)
+    FIELD("mix.o", l.o, W, HD)
+  }
+  if (d.ff == B200Q_FF_POLYNORM) {
+    FIELD("mlp.up", l.up, d.ff_dim, W)
+    FIELD("mlp.act", l.act, 1, 4)
+    FIELD("mlp.down", l.ff_down, W, d.ff_dim)
+  } else if (d.ff == B200Q_FF_MOE) {
+    FIELD("mlp.router", l.router, d.n_experts, W)
+    FIELD("mlp.router_bias", l.router_bias, 1, d.n_experts)
+    FIELD("mlp.experts_gate_up", l.experts_gate_up, (int64_t)d.n_experts * 2 * d.ff_dim, W)
+    FIELD("mlp.experts_down", l.experts_down, (int64_t)d.n_experts * W, d.ff_dim)
+    if (d.shared_dim > 0) {
+      FIELD("mlp.shared_gate_up", l.shared_gate_up, 2 * (int64_t)d.shared_dim, W)
+      FIELD("mlp.shared_down", l.shared_down, W, d.shared_dim)
+      FIELD("mlp.shared_gate", l.shared_gate, 1, W)
+    }
+  }
+#undef FIELD
+  set_error("bind_weight: layer %d has no weight '%s'", li, field);
+  return B200Q_EINVAL;
+}
+
+static int check_bound(b200q_model* m) {
+  if (!m->embed || !m->final_norm || !m->lm_head || !m->ws) {
+    set_error("forward: model not fully bound (embed/final_norm/lm_head/workspace)");
+    return B200Q_ESTATE;
+  }
+  bool need_kv = false, need_state = false;
+  for (size_t i = 0; i < m->lay->layers.size(); ++i) {
+    const b200q_layered_layer& l = m->lay->layers[i];
+    const b200q_layer_desc& d = l.d;
+    bool ok = l.norm1 && l.o && (d.ff == B200Q_FF_NONE || l.norm2);
+    if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
+      need_kv = true;
+      ok = ok && l.down && l.q_norm && (d.kv_from >= 0 || l.kv_norm) && l.uq && l.uk_t && l.uv;
+    } else {
+      need_state = true;
+      ok = ok && l.proj && l.w2 && l.w0 && l.a_bias && l.out_norm;
+    }
+    if (d.ff == B200Q_FF_POLYNORM) ok = ok && l.up && l.act && l.ff_down;
+    if (d.ff == B200Q_FF_MOE)
+      ok = ok && l.router && l.router_bias && l.experts_gate_up && l.experts_down &&
+           (d.shared_dim == 0 || (l.shared_gate_up && l.shared_down && l.shared_gate));
+    if (!ok) {
+      set_error("forward: layer %d has unbound weights", (int)i);
+      return B200Q_ESTATE;
+    }
+  }
+  if ((need_kv && !m->kv) || (need_state && !m->lay->state)) {
+    set_error("forward: cache / recurrent state not bound");
+    return B200Q_ESTATE;
+  }
+  return B200Q_OK;
+}
+
+int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
+  int rc = check_bound(m);
+  if (rc) return rc;
+  const b200q_model_config& c = m->cfg;
+  b200q_layered* y = m->lay;
+  const int T = b->T, W = c.hidden, dt = c.dtype, es = esize(c);
+  B200Q_CHECK_ARG(T >= 0 && T <= c.max_tokens, "forward: T=%d exceeds workspace (%d)", T, c.max_tokens);
+  B200Q_CHECK_ARG(b->n_sample >= 0 && b->n_sample <= (b->no_sampling ? logit_rows(c) : c.max_seqs),
+                  "forward: n_sample=%d exceeds the logits buffer", b->n_sample);
+  B200Q_CHECK_ARG(b->seq_desc && b->row_seq && b->n_rows > 0, "forward: a layered model needs the per-sequence "
+                  "view of the step (seq_desc / row_seq)");
+  if (T == 0) return B200Q_OK;
+  cudaStream_t cst = as_stream(stream);
+#define TRY(cat, work, call)                                \
+  do {                                                      \
+    int _e0 = -1;                                           \
+    if (m->profiling) {                                     \
+      _e0 = m->get_event();                                 \
+      cudaEventRecord(m->ev_pool[_e0], cst);                \
+    }                                                       \
+    rc = (call);                                            \
+    if (rc) return rc;                                      \
+    if (m->profiling) {                                     \
+      int _e1 = m->get_event();                             \
+      cudaEventRecord(m->ev_pool[_e1], cst);                \
+      m->spans.push_back({(cat), (double)(work), _e0, _e1}); \
+    }                                                       \
+  } while (0)
+#define LIN(Aptr, lda, Wptr, bias, Cptr, ldc, N, K, f32)                                                     \
+  TRY(B200Q_PROF_GEMM, 2.0 * T * (double)(N) * (K),                                                          \
+      b200q_linear((Aptr), (lda), (Wptr), (bias), (Cptr), (ldc), T, (N), (K), dt, (f32), stream))
+  const int EW = B200Q_PROF_ELEMENTWISE;
+
+  TRY(EW, (double)T * W * (es + 4),
+      b200q_embed_f32(b->token_ids, b->prev_out_ids, m->embed, y->x, T, W, c.embed_scale > 0.f ? c.embed_scale : 1.f,
+                      dt, stream));
+  for (int li = 0; li < c.n_layers; ++li) {
+    const b200q_layered_layer& l = y->layers[li];
+    const b200q_layer_desc& d = l.d;
+    const bool has_ff = d.ff != B200Q_FF_NONE;
+    TRY(EW, (double)T * W * (4 + 2 * es),
+        b200q_centered_rmsnorm(y->x, nullptr, l.norm1, l.norm2, y->h1, has_ff ? y->h2 : nullptr, T, W, c.rms_eps, dt,
+                               stream));
+    // ---- mixer ----
+    if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
+      const int R = d.kv_rank, P = d.rot_dim, RP = R + P, H = d.heads, QD = d.dim + P;
+      const bool own = d.kv_from < 0;
+      const int nd = d.q_rank + (own ? RP : 0);
+      uint8_t* cache = m->kv + m->num_blocks * l.cache_block_off;
+      LIN(y->h1, W, l.down, nullptr, y->proj, nd, nd, W, 0);
+      TRY(EW, (double)T * (nd + d.q_rank + RP) * es,
+          b200q_latent_prep(y->proj, nd, d.q_rank, R, P, d.rot_dims, l.freq, b->positions, b->slot_mapping, l.q_norm,
+                            l.kv_norm, y->cq, cache, own ? 1 : 0, T, c.rms_eps, dt, stream));
+      LIN(y->cq, d.q_rank, l.uq, nullptr, y->q, H * QD, H * QD, d.q_rank, 0);
+      TRY(EW, (double)T * H * P * (es + 4),
+          b200q_rope_pairs_q(y->q, H, d.dim, P, d.rot_dims, l.freq, b->positions, y->qa, R, T, dt, stream));
+      // the unrotated query of every head, carried into the latent space: qa[t,h,:R] = W_uk[h]^T q[t,h,:dim]
+      if (d.dim > 0)
+        TRY(B200Q_PROF_GEMM, 2.0 * T * H * (double)R * d.dim,
+            b200q_linear_batched(y->q, H * QD, QD, l.uk_t, (long long)R * d.dim, y->qa, H * RP, RP, T, R, d.dim, H, dt,
+                                 1, stream));
+      else
+        B200Q_CUDA(cudaMemsetAsync(y->qa, 0, (size_t)T * H * RP * 4, cst));
+      TRY(B200Q_PROF_DECODE_ATTN, 0.0,
+          b200q_latent_attn(y->qa, cache, b->block_table, b->bt_stride, b->row_seq, b->positions, T, H, R, P,
+                            c.block_size, d.window, d.attn_scale, y->olat, dt, stream));
+      TRY(B200Q_PROF_GEMM, 2.0 * T * H * (double)R * d.vdim,
+          b200q_linear_batched(y->olat, H * R, R, l.uv, (long long)d.vdim * R, y->attn, H * d.vdim, d.vdim, T, d.vdim, R,
+                               H, dt, 0, stream));
+      LIN(y->attn, H * d.vdim, l.o, nullptr, y->mix, W, W, H * d.vdim, 0);
+    } else {
+      const int HD = d.heads * d.dim, NP = 5 * HD + d.decay_rank;
+      LIN(y->h1, W, l.proj, nullptr, y->proj, NP, NP, W, 0);
+      TRY(B200Q_PROF_PREFILL_ATTN, 0.0,
+          b200q_delta_rule(y->proj, NP, l.w2, l.w0, l.a_bias, l.out_norm, y->state + l.state_off,
+                           y->state_slot_floats, b->seq_desc, b->n_rows, d.heads, d.dim, d.decay_rank, c.rms_eps,
+                           y->attn, dt, stream));
+      LIN(y->attn, HD, l.o, nullptr, y->mix, W, W, HD, 0);
+    }
+    // ---- feed-forward and the layer's sum ----
+    if (d.ff == B200Q_FF_POLYNORM) {
+      LIN(y->h2, W, l.up, nullptr, y->ffh, d.ff_dim, d.ff_dim, W, 0);
+      TRY(EW, 2.0 * T * d.ff_dim * es, b200q_polynorm(y->ffh, l.act, y->ffa, T, d.ff_dim, c.rms_eps, dt, stream));
+      LIN(y->ffa, d.ff_dim, l.ff_down, nullptr, y->ffo, W, W, d.ff_dim, 0);
+      TRY(EW, (double)T * W * (8 + 2 * es),
+          b200q_layer_sum(y->x, y->mix, y->ffo, nullptr, nullptr, nullptr, 0, nullptr, nullptr, T, W, dt, stream));
+    } else if (d.ff == B200Q_FF_MOE) {
+      const int E = d.n_experts, K = d.top_k, F = d.ff_dim, P = T * K;
+      LIN(y->h2, W, l.router, l.router_bias, y->rlog, E, E, W, 1);
+      TRY(EW, (double)T * E * 4,
+          b200q_moe_route(y->rlog, T, E, K, y->idx, y->wts, y->group_off, y->perm_tok, y->pair_pos, stream));
+      TRY(B200Q_PROF_GEMM, 2.0 * P * 2.0 * F * W,
+          b200q_linear_grouped(y->h2, W, y->perm_tok, l.experts_gate_up, 2LL * F * W, y->egu, 2 * F, y->group_off, E, P,
+                               2 * F, W, dt, stream));
+      TRY(EW, 3.0 * P * F * es, b200q_clamped_glu(y->egu, y->eact, P, F, d.expert_limit, dt, stream));
+      TRY(B200Q_PROF_GEMM, 2.0 * P * (double)F * W,
+          b200q_linear_grouped(y->eact, F, nullptr, l.experts_down, (long long)W * F, y->eout, W, y->group_off, E, P, W,
+                               F, dt, stream));
+      const bool sh = d.shared_dim > 0;
+      if (sh) {
+        const int FS = d.shared_dim;
+        LIN(y->h2, W, l.shared_gate_up, nullptr, y->ffh, 2 * FS, 2 * FS, W, 0);
+        TRY(EW, 3.0 * T * FS * es, b200q_clamped_glu(y->ffh, y->ffa, T, FS, d.shared_limit, dt, stream));
+        LIN(y->ffa, FS, l.shared_down, nullptr, y->shout, W, W, FS, 0);
+        LIN(y->h2, W, l.shared_gate, nullptr, y->sgate, 1, 1, W, 1);
+      }
+      TRY(EW, (double)T * W * (8 + (2 + K) * es),
+          b200q_layer_sum(y->x, y->mix, nullptr, y->eout, y->pair_pos, y->wts, K, sh ? y->shout : nullptr,
+                          sh ? y->sgate : nullptr, T, W, dt, stream));
+    } else {
+      TRY(EW, (double)T * W * (8 + es),
+          b200q_layer_sum(y->x, y->mix, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, T, W, dt, stream));
+    }
+    if (y->tap) TRY(EW, 8.0 * T * W, b200q_copy_f32(y->x, y->tap + (int64_t)li * T * W, (int64_t)T * W, stream));
+  }
+  if (b->n_sample > 0) {
+    const int n = b->n_sample;
+    TRY(EW, (double)n * W * (4 + es),
+        b200q_centered_rmsnorm(y->x, b->sample_rows, (const float*)m->final_norm, nullptr, y->sel, nullptr, n, W,
+                               c.rms_eps, dt, stream));
+    TRY(B200Q_PROF_GEMM, 2.0 * n * (double)c.vocab * W,
+        b200q_linear(y->sel, W, m->lm_head, nullptr, y->logits, c.vocab, n, c.vocab, W, dt, 1, stream));
+    if (!b->no_sampling) {
+      if (b->sample_params) {
+        TRY(EW, 6.0 * n * c.vocab, b200q_f32_to_bf16(y->logits, y->logits_bf16, (int64_t)n * c.vocab, stream));
+        TRY(EW, 2.0 * n * c.vocab, b200q_sample_bf16(y->logits_bf16, b->sample_params, b->out_ids, n, c.vocab, stream));
+      } else {
+        TRY(EW, 4.0 * n * c.vocab, b200q_argmax_f32(y->logits, b->out_ids, n, c.vocab, stream));
+      }
+    }
+  }
+#undef LIN
+#undef TRY
+  return B200Q_OK;
+}
+
+}  // namespace b200q
+
+extern "C" {
+
+int b200q_model_create_layered(const b200q_model_config* cfg, const b200q_layer_desc* layers, b200q_model_t* out) {
+  return layered_create(cfg, layers, out);
+}
+
+int64_t b200q_model_kv_block_bytes(b200q_model_t m) { return m && m->lay ? m->lay->kv_block_bytes : -1; }
+
+int64_t b200q_model_state_slot_bytes(b200q_model_t m) { return m && m->lay ? m->lay->state_slot_floats * 4 : -1; }
+
+int b200q_model_bind_state(b200q_model_t m, void* p, int64_t n_slots) {
+  B200Q_CHECK_ARG(m && m->lay && p && n_slots > 0, "bind_state: bad argument");
+  B200Q_CHECK_ARG((reinterpret_cast<uintptr_t>(p) & 15) == 0, "recurrent state must be 16-byte aligned");
+  m->lay->state = (float*)p;
+  m->lay->n_slots = n_slots;
+  return B200Q_OK;
+}
+
+const float* b200q_model_logits_f32_ptr(b200q_model_t m) { return m && m->lay ? m->lay->logits : nullptr; }
+
+int b200q_model_set_layer_tap(b200q_model_t m, float* p) {
+  B200Q_CHECK_ARG(m && m->lay, "set_layer_tap: not a layered model");
+  m->lay->tap = p;
+  return B200Q_OK;
+}
+
+}  // extern "C"

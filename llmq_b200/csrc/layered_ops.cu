@@ -1,0 +1,862 @@
+// layered_ops.cu — kernels of the layered architectures (B200Q_ARCH_RAMOPEL): fp32 residual stream,
+// zero-centred RMS norms, a shape-agnostic linear layer (plain / per-head batched / grouped by expert),
+// latent attention over a paged latent cache with a sliding window, the generalized delta-rule
+// recurrence over fp32 state slots, PolyNorm, clamped gated experts with top-k routing.
+//
+// Every kernel is a template over the element type of matrices, activations and cache (bf16 or
+// fp32); what has to be exact — residual sum, norms, scores and softmax, router, recurrent state,
+// decays and gates of the recurrence, angles — is fp32 (angles fp64) in both instantiations.
+// Nothing here depends on which other rows share the batch: every reduction runs in a fixed order
+// per row, so a token's result is the same alone, in a chunk or in a mixed batch.
+#include "common.cuh"
+
+namespace b200q {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// sum over the block (blockDim.x a multiple of 32, <= 1024); red: >= 32 floats of shared memory.
+// Every thread adds the warp partials in the same order, so all threads hold the same bits.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------------------
+// embedding into the fp32 residual: x[t,:] = table[id,:] * scale (ids < 0: see resolve in elementwise.cu)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) embed_f32_kernel(const int32_t* __restrict__ ids,
+                                                        const int32_t* __restrict__ prev_out,
+                                                        const T* __restrict__ table, float* __restrict__ out,
+                                                        int Tn, int W, float scale) {
+  const long long total = (long long)Tn * W;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / W), c = (int)(i % W);
+    int id = __ldg(ids + t);
+    if (id < 0) id = prev_out[-1 - id];
+    out[i] = ldf(table + (long long)id * W + c) * scale;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// zero-centred RMS norm of fp32 rows with up to two weights at once (the two branches of a parallel
+// layer read the same x):  y_k = x / sqrt(mean(x^2) + eps) * (1 + w_k).  rows != NULL: gather.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) centered_norm_kernel(const float* __restrict__ x,
+                                                            const int32_t* __restrict__ rows,
+                                                            const float* __restrict__ w1,
+                                                            const float* __restrict__ w2, T* __restrict__ y1,
+                                                            T* __restrict__ y2, int W, float eps) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const float* xr = x + (long long)(rows ? rows[r] : r) * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) ss += xr[c] * xr[c];
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = xr[c] * inv;
+    stf(y1 + (long long)r * W + c, v * (1.f + w1[c]));
+    if (y2) stf(y2 + (long long)r * W + c, v * (1.f + w2[c]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// linear layer for ANY shape: C[m,n] = sum_k A[m,k] W[n,k] (+ bias[n]), fp32 FMA accumulation in
+// ascending k (true fp32 for fp32 operands: no reduced-precision tensor mode).  blockIdx.z is either a
+// batch index (per-head weights: strides a_bs / w_bs / c_bs) or, with group_off != NULL, a group
+// (expert) that owns rows [group_off[z], group_off[z+1]) of C, reading A through a_rows if given.
+// 64x64x16 tiles, 256 threads, 4x4 outputs per thread.
+// ------------------------------------------------------------------------------------------------
+struct LinearArgs {
+  const void* A;
+  const void* W;
+  void* C;
+  const float* bias;
+  const int32_t* a_rows;
+  const int32_t* group_off;
+  long long a_bs, w_bs, c_bs;
+  int lda, ldc, M, N, K;
+};
+
+template <typename T, typename TC>
+__global__ void __launch_bounds__(256) linear_kernel(LinearArgs a) {
+  constexpr int BM = 64, BN = 64, BK = 16, LD = 68;
+  __shared__ __align__(16) float As[BK][LD];
+  __shared__ __align__(16) float Ws[BK][LD];
+  const int z = blockIdx.z;
+  int m_lo = 0, m_hi = a.M;
+  const T* A = (const T*)a.A;
+  const T* Wm = (const T*)a.W + (long long)z * a.w_bs;
+  TC* Cm = (TC*)a.C;
+  if (a.group_off) {
+    m_lo = a.group_off[z];
+    m_hi = a.group_off[z + 1];
+  } else {
+    A += (long long)z * a.a_bs;
+    Cm += (long long)z * a.c_bs;
+  }
+  const int m0 = m_lo + blockIdx.y * BM, n0 = blockIdx.x * BN;
+  if (m0 >= m_hi) return;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  // each thread stages 4 elements of A and of W per k-tile: element e = tid + 256*i -> (row e/16, k e%16)
+  long long a_off[4];
+  long long w_off[4];
+  bool a_ok[4], w_ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int e = tid + 256 * i, r = e >> 4;
+    const int m = m0 + r, n = n0 + r;
+    a_ok[i] = m < m_hi;
+    w_ok[i] = n < a.N;
+    const int src = a_ok[i] ? (a.a_rows ? a.a_rows[m] : m) : 0;
+    a_off[i] = (long long)src * a.lda;
+    w_off[i] = (long long)(w_ok[i] ? n : 0) * a.K;
+  }
+  for (int k0 = 0; k0 < a.K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = tid + 256 * i, r = e >> 4, kk = e & 15;
+      const bool kin = k0 + kk < a.K;
+      As[kk][r] = (a_ok[i] && kin) ? ldf(A + a_off[i] + k0 + kk) : 0.f;
+      Ws[kk][r] = (w_ok[i] && kin) ? ldf(Wm + w_off[i] + k0 + kk) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      const float4 wv = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
+      const float ar[4] = {av.x, av.y, av.z, av.w}, wr[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= m_hi) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < a.N) stf(Cm + (long long)m * a.ldc + n, acc[i][j] + (a.bias ? a.bias[n] : 0.f));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// latent attention, step 1 (one CTA per token).  proj = [query latent (q_rank) | kv latent (kv_rank) |
+// shared rotated key part (rot_dim)] as the fused down-projection wrote it.
+//   cq    = rmsnorm(query latent) * w_qn                                  -> cq [T, q_rank]
+//   cache = [ rmsnorm(kv latent) * w_kvn | rotate(key part, position) ]   -> row slot_mapping[t]
+// (has_kv = 0: the layer reads another layer's cache and only has the query part.)
+// Pairs (2i, 2i+1) of the first rot_dims entries turn by position * freq[i]; angle and sin/cos in fp64.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) latent_prep_kernel(const T* __restrict__ proj, int ldp, int q_rank,
+                                                          int kv_rank, int rot_dim, int rot_dims,
+                                                          const double* __restrict__ freq,
+                                                          const int32_t* __restrict__ positions,
+                                                          const int32_t* __restrict__ slot_mapping,
+                                                          const float* __restrict__ w_qn,
+                                                          const float* __restrict__ w_kvn, T* __restrict__ cq,
+                                                          T* __restrict__ cache, int has_kv, float eps) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const T* pr = proj + (long long)t * ldp;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) {
+    const float v = ldf(pr + c);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
+  for (int c = threadIdx.x; c < q_rank; c += blockDim.x)
+    stf(cq + (long long)t * q_rank + c, ldf(pr + c) * inv * w_qn[c]);
+  if (!has_kv) return;
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  T* row = cache + (long long)slot * (kv_rank + rot_dim);
+  const T* pc = pr + q_rank;
+  ss = 0.f;
+  for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+    const float v = ldf(pc + c);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  inv = 1.f / sqrtf(ss / (float)kv_rank + eps);
+  for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) stf(row + c, ldf(pc + c) * inv * w_kvn[c]);
+  const T* pk = pc + kv_rank;
+  const double pos = (double)positions[t];
+  for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
+    double sn, cs;
+    sincos(pos * freq[i], &sn, &cs);
+    const float u = ldf(pk + 2 * i), v = ldf(pk + 2 * i + 1), c = (float)cs, s = (float)sn;
+    stf(row + kv_rank + 2 * i, u * c - v * s);
+    stf(row + kv_rank + 2 * i + 1, v * c + u * s);
+  }
+  for (int c = rot_dims + threadIdx.x; c < rot_dim; c += blockDim.x) stf(row + kv_rank + c, ldf(pk + c));
+}
+
+// step 2 (one CTA per token): the rotated part of every head's query, turned by the token's position, goes
+// to its place behind the latent-space query: qa[t, h, kv_rank + j] (fp32).  q: [T, heads*(dim+rot_dim)].
+template <typename T>
+__global__ void __launch_bounds__(128) rope_q_kernel(const T* __restrict__ q, int heads, int dim, int rot_dim,
+                                                     int rot_dims, const double* __restrict__ freq,
+                                                     const int32_t* __restrict__ positions,
+                                                     float* __restrict__ qa, int kv_rank) {
+  extern __shared__ float cs_sn[];  // [rot_dims/2][2]
+  const int t = blockIdx.x, half = rot_dims / 2;
+  const double pos = (double)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double sn, cs;
+    sincos(pos * freq[i], &sn, &cs);
+    cs_sn[2 * i] = (float)cs;
+    cs_sn[2 * i + 1] = (float)sn;
+  }
+  __syncthreads();
+  const int RP = kv_rank + rot_dim;
+  for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
+    const int h = e / half, i = e % half;
+    const T* src = q + ((long long)t * heads + h) * (dim + rot_dim) + dim;
+    float* dst = qa + ((long long)t * heads + h) * RP + kv_rank;
+    const float u = ldf(src + 2 * i), v = ldf(src + 2 * i + 1), c = cs_sn[2 * i], s = cs_sn[2 * i + 1];
+    dst[2 * i] = u * c - v * s;
+    dst[2 * i + 1] = v * c + u * s;
+  }
+  const int rest = rot_dim - rot_dims;
+  for (int e = threadIdx.x; e < heads * rest; e += blockDim.x) {
+    const int h = e / rest, j = rot_dims + e % rest;
+    qa[((long long)t * heads + h) * RP + kv_rank + j] = ldf(q + ((long long)t * heads + h) * (dim + rot_dim) + dim + j);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// step 3: attention in the latent space.  The query of head h is qa[t,h,:] = [W_uk[h]^T q_unrotated |
+// q_rotated] (kv_rank + rot_dim values), a cached row is [latent c | rotated key part], so the score is
+// one dot product against the cached row and the value is the latent itself:
+//     out[t,h,:] = softmax_j( scale * qa[t,h] . row_j ) . c_j      over  max(0, p-window+1) <= j <= p
+// (the per-head value up-projection is applied to out afterwards).  One CTA per (token, group of 8
+// heads); a chunk of 32 cached rows is staged in shared memory once and used by all 8 heads (warp =
+// head, lane = key for the scores, lane = output dims for the weighted sum); online softmax in fp32.
+// The chunks start at the window's first key, so the arithmetic of a token does not depend on how the
+// prompt was cut or batched.  kv_rank <= 32 * LATENT_ACC.
+// ------------------------------------------------------------------------------------------------
+constexpr int LATENT_ACC = 16;
+template <typename T>
+__global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restrict__ qa,
+                                                          const T* __restrict__ cache,
+                                                          const int32_t* __restrict__ block_table, int bt_stride,
+                                                          const int32_t* __restrict__ row_seq,
+                                                          const int32_t* __restrict__ positions, int heads,
+                                                          int kv_rank, int rot_dim, int block_size, int window,
+                                                          float scale, T* __restrict__ out) {
+  extern __shared__ float sm[];
+  const int RP = kv_rank + rot_dim, KS = RP + 1;
+  float* qs = sm;            // [8][RP]
+  float* ks = sm + 8 * RP;   // [32][RP+1]
+  const int t = blockIdx.x, h0 = blockIdx.y * 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = h0 + warp;
+  const bool live = h < heads;
+  const int p = positions[t];
+  const int32_t* bt = block_table + (long long)row_seq[t] * bt_stride;
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  for (int e = threadIdx.x; e < 8 * RP; e += blockDim.x) {
+    const int hh = h0 + e / RP;
+    qs[e] = hh < heads ? qa[((long long)t * heads + hh) * RP + e % RP] : 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  float acc[LATENT_ACC];
+#pragma unroll
+  for (int i = 0; i < LATENT_ACC; ++i) acc[i] = 0.f;
+  const float* qh = qs + warp * RP;
+  for (int j0 = lo; j0 <= p; j0 += 32) {
+    const int n = min(32, p + 1 - j0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * RP; e += blockDim.x) {
+      const int j = e / RP, d = e % RP, pos = j0 + j;
+      const long long row = (long long)bt[pos / block_size] * block_size + pos % block_size;
+      ks[j * KS + d] = ldf(cache + row * RP + d);
+    }
+    __syncthreads();
+    if (!live) continue;
+    float s = -INFINITY;
+    if (lane < n) {
+      const float* kr = ks + lane * KS;
+      float dot = 0.f;
+      for (int d = 0; d < RP; ++d) dot = fmaf(qh[d], kr[d], dot);
+      s = dot * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);  // m = -inf on the first chunk: exp(-inf) = 0
+    const float pl = lane < n ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(pl);
+#pragma unroll
+    for (int i = 0; i < LATENT_ACC; ++i) acc[i] *= corr;
+    for (int j = 0; j < n; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, pl, j);
+      const float* kr = ks + j * KS;
+#pragma unroll
+      for (int i = 0; i < LATENT_ACC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < kv_rank) acc[i] = fmaf(pj, kr[d], acc[i]);
+      }
+    }
+    m = m_new;
+  }
+  if (!live) return;
+  const float inv = 1.f / l;
+  T* o = out + ((long long)t * heads + h) * kv_rank;
+#pragma unroll
+  for (int i = 0; i < LATENT_ACC; ++i) {
+    const int d = lane + 32 * i;
+    if (d < kv_rank) stf(o + d, acc[i] * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// generalized delta rule.  One CTA per (sequence, head), thread j owns column j of the state S[key][value]
+// (kept in shared memory for the tokens of this step, loaded from / stored to the sequence's fp32 state
+// slot; a sequence whose first token this step is position 0 starts from zero, whatever the slot held).
+// proj row = [r | k | v | g | a | z] (heads*dim each, z = decay_rank).  Per token, per head:
+//   decay w_i = exp(-e^-1/2 * sigmoid(w0_i + sum_r w2[i,r] tanh(z_r))),  a_i = sigmoid(a_i + a_bias_i),
+//   u = k / sqrt(sum k^2 + 1e-6)
+//   S <- diag(w) S - (a*u) (u^T S) + k v^T          (both terms read the old S)
+//   o = S^T r;  out = o / sqrt(mean(o^2) + eps) * out_norm * sigmoid(g)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void delta_rule_kernel(const T* __restrict__ proj, int ldp, const T* __restrict__ w2,
+                                  const float* __restrict__ w0, const float* __restrict__ a_bias,
+                                  const float* __restrict__ out_norm, float* __restrict__ state,
+                                  long long slot_stride, const int32_t* __restrict__ seq_desc, int heads, int D,
+                                  int Rk, float eps, T* __restrict__ out) {
+  extern __shared__ float sm[];
+  float* S = sm;                  // [D][D]
+  float* kv_ = S + D * D;         // k
+  float* us = kv_ + D;            // unit key
+  float* aus = us + D;            // a * u
+  float* wd = aus + D;            // decay
+  float* rs = wd + D;             // receptance
+  float* w2s = rs + D;            // [Rk][D]
+  float* zt = w2s + (long long)Rk * D;  // [Rk]
+  float* red = zt + Rk;           // [32]
+  const int seq = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
+  const int row0 = seq_desc[4 * seq + 0], n = seq_desc[4 * seq + 1], pos0 = seq_desc[4 * seq + 2],
+            slot = seq_desc[4 * seq + 3];
+  const int HD = heads * D, c = h * D + i;
+  const bool on = i < D;
+  float* st = state + (long long)slot * slot_stride + (long long)h * D * D;
+  for (int e = i; e < D * D; e += blockDim.x) S[e] = pos0 > 0 ? st[e] : 0.f;
+  for (int e = i; e < Rk * D; e += blockDim.x) {
+    const int r = e / D, ch = e % D;
+    w2s[e] = ldf(w2 + (long long)(h * D + ch) * Rk + r);
+  }
+  const float w0c = on ? w0[c] : 0.f, abc = on ? a_bias[c] : 0.f, onc = on ? out_norm[c] : 0.f;
+  for (int tt = 0; tt < n; ++tt) {
+    const T* pr = proj + (long long)(row0 + tt) * ldp;
+    for (int r = i; r < Rk; r += blockDim.x) zt[r] = tanhf(ldf(pr + 5 * HD + r));
+    __syncthreads();
+    float kk = 0.f, wv = 0.f, av = 0.f, rv = 0.f;
+    if (on) {
+      kk = ldf(pr + HD + c);
+      rv = ldf(pr + c);
+      float z = w0c;
+      for (int r = 0; r < Rk; ++r) z = fmaf(w2s[r * D + i], zt[r], z);
+      wv = expf(-0.6065306597126334f * sigmoidf_(z));
+      av = sigmoidf_(ldf(pr + 4 * HD + c) + abc);
+    }
+    const float ssk = block_sum(kk * kk, red);
+    if (on) {
+      const float uu = kk / sqrtf(ssk + 1e-6f);
+      kv_[i] = kk;
+      us[i] = uu;
+      aus[i] = av * uu;
+      wd[i] = wv;
+      rs[i] = rv;
+    }
+    __syncthreads();
+    float o = 0.f;
+    if (on) {
+      const float vj = ldf(pr + 2 * HD + c);
+      float uS = 0.f;
+      for (int q = 0; q < D; ++q) uS = fmaf(us[q], S[q * D + i], uS);
+      for (int q = 0; q < D; ++q) {
+        const float s = wd[q] * S[q * D + i] - aus[q] * uS + kv_[q] * vj;
+        S[q * D + i] = s;
+        o = fmaf(s, rs[q], o);
+      }
+    }
+    const float sso = block_sum(o * o, red);
+    if (on) {
+      const float y = o / sqrtf(sso / (float)D + eps) * onc * sigmoidf_(ldf(pr + 3 * HD + c));
+      stf(out + (long long)(row0 + tt) * HD + c, y);
+    }
+  }
+  __syncthreads();
+  for (int e = i; e < D * D; e += blockDim.x) st[e] = S[e];
+}
+
+// ------------------------------------------------------------------------------------------------
+// PolyNorm: y = a N(z) + b N(z^2) + c N(z^3) + e, N(v) = v / sqrt(mean(v^2) + eps) over the row
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) polynorm_kernel(const T* __restrict__ z, const float* __restrict__ coef,
+                                                       T* __restrict__ y, int F, float eps) {
+  __shared__ float red[32];
+  const T* zr = z + (long long)blockIdx.x * F;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int c = threadIdx.x; c < F; c += blockDim.x) {
+    const float v = ldf(zr + c), v2 = v * v;
+    s2 += v2;
+    s4 += v2 * v2;
+    s6 += v2 * v2 * v2;
+  }
+  s2 = block_sum(s2, red);
+  s4 = block_sum(s4, red);
+  s6 = block_sum(s6, red);
+  const float i1 = coef[0] / sqrtf(s2 / (float)F + eps), i2 = coef[1] / sqrtf(s4 / (float)F + eps),
+              i3 = coef[2] / sqrtf(s6 / (float)F + eps), e = coef[3];
+  for (int c = threadIdx.x; c < F; c += blockDim.x) {
+    const float v = ldf(zr + c);
+    stf(y + (long long)blockIdx.x * F + c, v * i1 + v * v * i2 + v * v * v * i3 + e);
+  }
+}
+
+// clamped gated unit: gu = [gate (F) | up (F)] per row; y = g' sigmoid(1.702 g') (u' + 1),
+// g' = min(g, limit), u' = clamp(u, -limit, limit)
+template <typename T>
+__global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ y,
+                                                          long long rows, int F, float limit) {
+  const long long total = rows * F;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long long)gridDim.x * blockDim.x) {
+    const long long r = e / F;
+    const int c = (int)(e % F);
+    const float g = fminf(ldf(gu + r * 2 * F + c), limit);
+    const float u = fminf(fmaxf(ldf(gu + r * 2 * F + F + c), -limit), limit);
+    stf(y + e, g * sigmoidf_(1.702f * g) * (u + 1.f));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// top-k routing: one warp per token over fp32 router logits [T, E]; the k largest (ties: lowest index),
+// weights = softmax over the chosen logits.  k <= 32.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int Tn, int E, int top,
+                                                        int32_t* __restrict__ idx, float* __restrict__ wts) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= Tn) return;
+  const float* z = logits + (long long)t * E;
+  float chosen_v = 0.f;  // lane k keeps the k-th choice
+  int chosen_i = -1;
+  float prev_v = INFINITY;
+  int prev_i = -1;
+  for (int k = 0; k < top; ++k) {
+    // the largest (value, -index) strictly below the previous choice in that order
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      const bool below = v < prev_v || (v == prev_v && e > prev_i);
+      if (below && (v > bv || (v == bv && e < bi))) {
+        bv = v;
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == k) {
+      chosen_v = bv;
+      chosen_i = bi;
+    }
+    prev_v = bv;
+    prev_i = bi;
+  }
+  const float top_v = __shfl_sync(0xffffffffu, chosen_v, 0);
+  const float ex = lane < top ? expf(chosen_v - top_v) : 0.f;
+  const float sum = warp_sum(ex);
+  if (lane < top) {
+    idx[(long long)t * top + lane] = chosen_i;
+    wts[(long long)t * top + lane] = ex / sum;
+  }
+}
+
+// grouping of the (token, choice) pairs by expert for the grouped linear layers (one CTA):
+// group_off[E+1], perm_tok[pos] = token of the pair at sorted position pos, pair_pos[pair] = pos.
+// The order inside a group comes from atomics and may differ between runs; rows are independent, so
+// no result depends on it.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int32_t* __restrict__ idx, int P, int top, int E,
+                                                        int32_t* __restrict__ group_off,
+                                                        int32_t* __restrict__ perm_tok,
+                                                        int32_t* __restrict__ pair_pos) {
+  extern __shared__ int32_t si[];  // counts[E] | offs[E+1] | cursor[E]
+  int32_t* counts = si;
+  int32_t* offs = si + E;
+  int32_t* cursor = offs + E + 1;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = cursor[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&counts[idx[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      offs[e] = run;
+      run += counts[e];
+    }
+    offs[E] = run;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) group_off[e] = offs[e];
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = idx[p];
+    const int pos = offs[e] + atomicAdd(&cursor[e], 1);
+    perm_tok[pos] = p / top;
+    pair_pos[p] = pos;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// end of a parallel layer: x += mixer + ff, with ff either a dense branch (f) or the routed sum
+//   sum_k wts[t,k] * expert_out[pair_pos[t*top+k], :]  (+ sigmoid(shared_gate[t]) * shared_out[t, :])
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) layer_sum_kernel(float* __restrict__ x, const T* __restrict__ mix,
+                                                        const T* __restrict__ f, const T* __restrict__ expert_out,
+                                                        const int32_t* __restrict__ pair_pos,
+                                                        const float* __restrict__ wts, int top,
+                                                        const T* __restrict__ shared_out,
+                                                        const float* __restrict__ shared_gate, int Tn, int W) {
+  const long long total = (long long)Tn * W;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(e / W), c = (int)(e % W);
+    float ff = 0.f;
+    if (f) ff = ldf(f + e);
+    if (expert_out) {
+      for (int k = 0; k < top; ++k)
+        ff = fmaf(wts[(long long)t * top + k], ldf(expert_out + (long long)pair_pos[(long long)t * top + k] * W + c), ff);
+      if (shared_out) ff = fmaf(sigmoidf_(shared_gate[t]), ldf(shared_out + e), ff);
+    }
+    x[e] += ldf(mix + e) + ff;
+  }
+}
+
+// greedy sampler over fp32 logits (lowest index wins ties) and the bf16 copy the temperature sampler reads
+__global__ void __launch_bounds__(256) argmax_f32_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids,
+                                                         int V) {
+  __shared__ float bv[256];
+  __shared__ int bi[256];
+  const float* z = logits + (long long)blockIdx.x * V;
+  float v = -INFINITY;
+  int ix = 0x7fffffff;
+  for (int c = threadIdx.x; c < V; c += blockDim.x)
+    if (z[c] > v || (z[c] == v && c < ix)) {
+      v = z[c];
+      ix = c;
+    }
+  bv[threadIdx.x] = v;
+  bi[threadIdx.x] = ix;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      const float ov = bv[threadIdx.x + o];
+      const int oi = bi[threadIdx.x + o];
+      if (ov > bv[threadIdx.x] || (ov == bv[threadIdx.x] && oi < bi[threadIdx.x])) {
+        bv[threadIdx.x] = ov;
+        bi[threadIdx.x] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) ids[blockIdx.x] = bi[0] == 0x7fffffff ? 0 : bi[0];
+}
+__global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* __restrict__ in, bf16* __restrict__ out,
+                                                          long long n) {
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x)
+    out[e] = __float2bfloat16_rn(in[e]);
+}
+__global__ void __launch_bounds__(256) copy_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                       long long n) {
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long long)gridDim.x * blockDim.x)
+    out[e] = in[e];
+}
+
+static inline int grid_for(long long total, int block = 256) {
+  long long g = (total + block - 1) / block;
+  return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
+}
+static inline bool is_dtype(int d) { return d == B200Q_DTYPE_BF16 || d == B200Q_DTYPE_F32; }
+
+}  // namespace b200q
+
+using namespace b200q;
+
+#define DISPATCH_T(dtype, ...)                   \
+  do {                                           \
+    if ((dtype) == B200Q_DTYPE_F32) {            \
+      using T = float;                           \
+      __VA_ARGS__;                               \
+    } else {                                     \
+      using T = bf16;                            \
+      __VA_ARGS__;                               \
+    }                                            \
+  } while (0)
+
+extern "C" {
+
+int b200q_embed_f32(const int32_t* ids, const int32_t* prev_out, const void* table, float* out, int T_, int W,
+                    float scale, int dtype, void* stream) {
+  B200Q_CHECK_ARG(ids && table && out && T_ >= 0 && W > 0 && is_dtype(dtype), "embed_f32: bad argument");
+  if (T_ == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (embed_f32_kernel<T><<<grid_for((long long)T_ * W), 256, 0, as_stream(stream)>>>(
+                        ids, prev_out, (const T*)table, out, T_, W, scale)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_centered_rmsnorm(const float* x, const int32_t* rows, const float* w1, const float* w2, void* y1,
+                           void* y2, int n, int W, float eps, int dtype, void* stream) {
+  B200Q_CHECK_ARG(x && w1 && y1 && (!y2 || w2) && n >= 0 && W > 0 && is_dtype(dtype),
+                  "centered_rmsnorm: bad argument");
+  if (n == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (centered_norm_kernel<T><<<n, 256, 0, as_stream(stream)>>>(x, rows, w1, w2, (T*)y1, (T*)y2, W, eps)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+// the general form behind b200q_linear / _batched / _grouped
+static int launch_linear(const LinearArgs& a, int tiles_m, int nz, int dtype, int out_f32, void* stream) {
+  if (tiles_m <= 0 || nz <= 0 || a.N <= 0) return B200Q_OK;
+  dim3 grid((a.N + 63) / 64, tiles_m, nz);
+  B200Q_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "linear: grid too large (rows=%d groups=%d)", a.M, nz);
+  if (dtype == B200Q_DTYPE_F32) {
+    linear_kernel<float, float><<<grid, 256, 0, as_stream(stream)>>>(a);
+  } else if (out_f32) {
+    linear_kernel<bf16, float><<<grid, 256, 0, as_stream(stream)>>>(a);
+  } else {
+    linear_kernel<bf16, bf16><<<grid, 256, 0, as_stream(stream)>>>(a);
+  }
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_linear(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N, int K,
+                 int dtype, int out_f32, void* stream) {
+  B200Q_CHECK_ARG(A && W && C && M >= 0 && N > 0 && K > 0 && lda >= K && ldc >= N && is_dtype(dtype),
+                  "linear: bad argument (M=%d N=%d K=%d lda=%d ldc=%d)", M, N, K, lda, ldc);
+  if (M == 0) return B200Q_OK;
+  // shapes the tcgen05 GEMM takes go to the tensor cores
+  if (dtype == B200Q_DTYPE_BF16 && !out_f32 && !bias && lda == K && ldc == N && K % 64 == 0 && N % 64 == 0 &&
+      ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C)) & 15) == 0)
+    return b200q_gemm_bf16(A, W, C, M, N, K, stream);
+  LinearArgs a{A, W, C, bias, nullptr, nullptr, 0, 0, 0, lda, ldc, M, N, K};
+  return launch_linear(a, (M + 63) / 64, 1, dtype, out_f32, stream);
+}
+
+int b200q_linear_batched(const void* A, int lda, long long a_bs, const void* W, long long w_bs, void* C, int ldc,
+                         long long c_bs, int M, int N, int K, int batch, int dtype, int out_f32, void* stream) {
+  B200Q_CHECK_ARG(A && W && C && M >= 0 && N > 0 && K > 0 && batch > 0 && is_dtype(dtype),
+                  "linear_batched: bad argument");
+  if (M == 0) return B200Q_OK;
+  LinearArgs a{A, W, C, nullptr, nullptr, nullptr, a_bs, w_bs, c_bs, lda, ldc, M, N, K};
+  return launch_linear(a, (M + 63) / 64, batch, dtype, out_f32, stream);
+}
+
+int b200q_linear_grouped(const void* A, int lda, const int32_t* a_rows, const void* W, long long w_gs, void* C,
+                         int ldc, const int32_t* group_off, int groups, int max_rows, int N, int K, int dtype,
+                         void* stream) {
+  B200Q_CHECK_ARG(A && W && C && group_off && groups > 0 && max_rows >= 0 && N > 0 && K > 0 && is_dtype(dtype),
+                  "linear_grouped: bad argument");
+  if (max_rows == 0) return B200Q_OK;
+  LinearArgs a{A, W, C, nullptr, a_rows, group_off, 0, w_gs, 0, lda, ldc, max_rows, N, K};
+  return launch_linear(a, (max_rows + 63) / 64, groups, dtype, 0, stream);
+}
+
+int b200q_latent_prep(const void* proj, int ldp, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                      const double* freq, const int32_t* positions, const int32_t* slot_mapping,
+                      const float* w_qn, const float* w_kvn, void* cq, void* cache, int has_kv, int T_, float eps,
+                      int dtype, void* stream) {
+  B200Q_CHECK_ARG(proj && w_qn && cq && positions && q_rank > 0 && is_dtype(dtype) && T_ >= 0,
+                  "latent_prep: bad argument");
+  B200Q_CHECK_ARG(!has_kv || (cache && slot_mapping && w_kvn && freq && kv_rank > 0 && rot_dim >= 0 &&
+                              rot_dims % 2 == 0 && rot_dims <= rot_dim),
+                  "latent_prep: bad cache arguments (kv_rank=%d rot_dim=%d rot_dims=%d)", kv_rank, rot_dim, rot_dims);
+  if (T_ == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (latent_prep_kernel<T><<<T_, 128, 0, as_stream(stream)>>>(
+                        (const T*)proj, ldp, q_rank, kv_rank, rot_dim, rot_dims, freq, positions, slot_mapping, w_qn,
+                        w_kvn, (T*)cq, (T*)cache, has_kv, eps)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_rope_pairs_q(const void* q, int heads, int dim, int rot_dim, int rot_dims, const double* freq,
+                       const int32_t* positions, float* qa, int kv_rank, int T_, int dtype, void* stream) {
+  B200Q_CHECK_ARG(q && freq && positions && qa && heads > 0 && dim >= 0 && rot_dims % 2 == 0 && rot_dims <= rot_dim &&
+                      is_dtype(dtype) && T_ >= 0,
+                  "rope_pairs_q: bad argument");
+  if (T_ == 0 || rot_dim == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (rope_q_kernel<T><<<T_, 128, (size_t)(rot_dims + 2) * sizeof(float), as_stream(stream)>>>(
+                        (const T*)q, heads, dim, rot_dim, rot_dims, freq, positions, qa, kv_rank)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_latent_attn(const float* qa, const void* cache, const int32_t* block_table, int bt_stride,
+                      const int32_t* row_seq, const int32_t* positions, int T_, int heads, int kv_rank, int rot_dim,
+                      int block_size, int window, float scale, void* out, int dtype, void* stream) {
+  B200Q_CHECK_ARG(qa && cache && block_table && row_seq && positions && out && heads > 0 && T_ >= 0 &&
+                      block_size > 0 && window >= 0 && is_dtype(dtype),
+                  "latent_attn: bad argument");
+  B200Q_CHECK_ARG(kv_rank > 0 && kv_rank <= 32 * LATENT_ACC, "latent_attn: kv_rank=%d unsupported (1..%d)", kv_rank,
+                  32 * LATENT_ACC);
+  if (T_ == 0) return B200Q_OK;
+  const int RP = kv_rank + rot_dim;
+  const size_t smem = (size_t)(8 * RP + 32 * (RP + 1)) * sizeof(float);
+  B200Q_CHECK_ARG(smem <= 227 * 1024, "latent_attn: kv_rank + rot_dim = %d does not fit shared memory", RP);
+  dim3 grid(T_, (heads + 7) / 8);
+  if (dtype == B200Q_DTYPE_F32) {
+    B200Q_CUDA(cudaFuncSetAttribute(latent_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    latent_attn_kernel<float><<<grid, 256, smem, as_stream(stream)>>>(qa, (const float*)cache, block_table, bt_stride,
+                                                                      row_seq, positions, heads, kv_rank, rot_dim,
+                                                                      block_size, window, scale, (float*)out);
+  } else {
+    B200Q_CUDA(cudaFuncSetAttribute(latent_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    latent_attn_kernel<bf16><<<grid, 256, smem, as_stream(stream)>>>(qa, (const bf16*)cache, block_table, bt_stride,
+                                                                     row_seq, positions, heads, kv_rank, rot_dim,
+                                                                     block_size, window, scale, (bf16*)out);
+  }
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_delta_rule(const void* proj, int ldp, const void* w2, const float* w0, const float* a_bias,
+                     const float* out_norm, float* state, long long slot_stride, const int32_t* seq_desc,
+                     int n_seqs, int heads, int D, int Rk, float eps, void* out, int dtype, void* stream) {
+  B200Q_CHECK_ARG(proj && w2 && w0 && a_bias && out_norm && state && seq_desc && out && heads > 0 && D > 0 &&
+                      Rk > 0 && n_seqs >= 0 && is_dtype(dtype),
+                  "delta_rule: bad argument");
+  if (n_seqs == 0) return B200Q_OK;
+  const int threads = (D + 31) & ~31;
+  B200Q_CHECK_ARG(threads <= 1024, "delta_rule: dim=%d unsupported (<= 1024)", D);
+  const size_t smem = ((size_t)D * D + 5 * (size_t)D + (size_t)Rk * D + Rk + 32) * sizeof(float);
+  B200Q_CHECK_ARG(smem <= 227 * 1024, "delta_rule: a %dx%d state (+ rank %d) does not fit shared memory", D, D, Rk);
+  dim3 grid(n_seqs, heads);
+  if (dtype == B200Q_DTYPE_F32) {
+    B200Q_CUDA(cudaFuncSetAttribute(delta_rule_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    delta_rule_kernel<float><<<grid, threads, smem, as_stream(stream)>>>(
+        (const float*)proj, ldp, (const float*)w2, w0, a_bias, out_norm, state, slot_stride, seq_desc, heads, D, Rk,
+        eps, (float*)out);
+  } else {
+    B200Q_CUDA(cudaFuncSetAttribute(delta_rule_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    delta_rule_kernel<bf16><<<grid, threads, smem, as_stream(stream)>>>(
+        (const bf16*)proj, ldp, (const bf16*)w2, w0, a_bias, out_norm, state, slot_stride, seq_desc, heads, D, Rk, eps,
+        (bf16*)out);
+  }
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_polynorm(const void* z, const float* coef, void* y, int rows, int F, float eps, int dtype, void* stream) {
+  B200Q_CHECK_ARG(z && coef && y && rows >= 0 && F > 0 && is_dtype(dtype), "polynorm: bad argument");
+  if (rows == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (polynorm_kernel<T><<<rows, 256, 0, as_stream(stream)>>>((const T*)z, coef, (T*)y, F, eps)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_clamped_glu(const void* gate_up, void* y, int64_t rows, int F, float limit, int dtype, void* stream) {
+  B200Q_CHECK_ARG(gate_up && y && rows >= 0 && F > 0 && is_dtype(dtype), "clamped_glu: bad argument");
+  if (rows == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (clamped_glu_kernel<T><<<grid_for(rows * F), 256, 0, as_stream(stream)>>>((const T*)gate_up, (T*)y,
+                                                                                            rows, F, limit)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_moe_route(const float* logits, int T_, int E, int top, int32_t* idx, float* wts, int32_t* group_off,
+                    int32_t* perm_tok, int32_t* pair_pos, void* stream) {
+  B200Q_CHECK_ARG(logits && idx && wts && group_off && perm_tok && pair_pos && T_ >= 0 && E > 0 && top > 0 &&
+                      top <= 32 && top <= E && E <= 4096,
+                  "moe_route: bad argument (E=%d top=%d)", E, top);
+  if (T_ == 0) return B200Q_OK;
+  moe_route_kernel<<<(T_ + 3) / 4, 128, 0, as_stream(stream)>>>(logits, T_, E, top, idx, wts);
+  B200Q_LAUNCH_CHECK();
+  moe_plan_kernel<<<1, 1024, (size_t)(3 * E + 1) * sizeof(int32_t), as_stream(stream)>>>(idx, T_ * top, top, E,
+                                                                                          group_off, perm_tok, pair_pos);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_layer_sum(float* x, const void* mix, const void* f, const void* expert_out, const int32_t* pair_pos,
+                    const float* wts, int top, const void* shared_out, const float* shared_gate, int T_, int W,
+                    int dtype, void* stream) {
+  B200Q_CHECK_ARG(x && mix && T_ >= 0 && W > 0 && is_dtype(dtype) && (!expert_out || (pair_pos && wts && top > 0)) &&
+                      (!shared_out || shared_gate),
+                  "layer_sum: bad argument");
+  if (T_ == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (layer_sum_kernel<T><<<grid_for((long long)T_ * W), 256, 0, as_stream(stream)>>>(
+                        x, (const T*)mix, (const T*)f, (const T*)expert_out, pair_pos, wts, top, (const T*)shared_out,
+                        shared_gate, T_, W)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_argmax_f32(const float* logits, int32_t* ids, int B, int V, void* stream) {
+  B200Q_CHECK_ARG(logits && ids && B >= 0 && V > 0, "argmax_f32: bad argument");
+  if (B == 0) return B200Q_OK;
+  argmax_f32_kernel<<<B, 256, 0, as_stream(stream)>>>(logits, ids, V);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_f32_to_bf16(const float* in, void* out, int64_t n, void* stream) {
+  B200Q_CHECK_ARG(in && out && n >= 0, "f32_to_bf16: bad argument");
+  if (n == 0) return B200Q_OK;
+  f32_to_bf16_kernel<<<grid_for(n), 256, 0, as_stream(stream)>>>(in, (bf16*)out, n);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_copy_f32(const float* in, float* out, int64_t n, void* stream) {
+  B200Q_CHECK_ARG(in && out && n >= 0, "copy_f32: bad argument");
+  if (n == 0) return B200Q_OK;
+  copy_f32_kernel<<<grid_for(n), 256, 0, as_stream(stream)>>>(in, out, n);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+}  // extern "C"

@@ -12,55 +12,18 @@
 #include <vector>
 
 #include "common.cuh"
+#include "model_types.cuh"
 
 using namespace b200q;
 
-struct b200q_layer {
-  const void* input_norm = nullptr;
-  const void* qkv = nullptr;
-  const void* o = nullptr;
-  const void* post_norm = nullptr;  // llama: post_attention_layernorm (= the pre-MLP norm)
-  const void* gate_up = nullptr;
-  const void* down = nullptr;
-  // gemma2: the sandwich norms
-  const void* post_attn_norm = nullptr;
-  const void* pre_ffn_norm = nullptr;
-  const void* post_ffn_norm = nullptr;
-};
-
-struct b200q_model {
-  b200q_model_config cfg;
-  const void* embed = nullptr;
-  const void* final_norm = nullptr;
-  const void* lm_head = nullptr;
-  std::vector<b200q_layer> layers;
-  uint8_t* kv = nullptr;
-  int64_t num_blocks = 0;
-  const void* rope = nullptr;
-  // workspace views
-  uint8_t* ws = nullptr;
-  int64_t ws_bytes = 0;
-  // (no [T, 2I] gate_up buffer: the SwiGLU is applied in the gate_up GEMM's epilogue)
-  bf16 *x = nullptr, *residual = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr,
-       *sel = nullptr, *logits = nullptr;
-  // fold the split-K reduce of decode-sized projections into the consuming kernel (B200Q_FUSE_SPLITK=0: off)
-  bool fuse_splitk = true;
-  // optional per-category device timing (CUDA events on the forward's stream)
-  bool profiling = false;
-  std::vector<cudaEvent_t> ev_pool;
-  struct Span { int cat; double work; int e0, e1; };
-  std::vector<Span> spans;
-  int ev_used = 0;
-  b200q_profile prof{};
-  int get_event() {
-    if (ev_used == (int)ev_pool.size()) {
-      cudaEvent_t e;
-      cudaEventCreate(&e);
-      ev_pool.push_back(e);
-    }
-    return ev_used++;
-  }
-};
+namespace b200q {
+int layered_create(const b200q_model_config* cfg, const b200q_layer_desc* layers, b200q_model_t* out);
+void layered_destroy(b200q_model* m);
+int64_t layered_workspace_bytes(b200q_model* m);
+int layered_bind_workspace(b200q_model* m, void* p, int64_t bytes);
+int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t rows, int64_t cols);
+int layered_forward(b200q_model* m, const b200q_batch* b, void* stream);
+}  // namespace b200q
 
 static inline int64_t align256(int64_t v) { return (v + 255) & ~(int64_t)255; }
 
@@ -72,6 +35,7 @@ static int check_cfg(const b200q_model_config* c) {
   B200Q_CHECK_ARG(c != nullptr, "model config is null");
   B200Q_CHECK_ARG(c->hidden > 0 && c->hidden % 64 == 0 && c->hidden <= 8192,
                   "hidden=%d unsupported (multiple of 64, <= 8192)", c->hidden);
+  B200Q_CHECK_ARG(c->arch != B200Q_ARCH_RAMOPEL, "a layered architecture is created with b200q_model_create_layered");
   B200Q_CHECK_ARG(c->arch == B200Q_ARCH_LLAMA || c->arch == B200Q_ARCH_GEMMA2, "arch=%d unknown", c->arch);
   B200Q_CHECK_ARG(c->head_dim == 64 || c->head_dim == 128 || c->head_dim == 256,
                   "head_dim=%d unsupported (64, 128, 256)", c->head_dim);
@@ -131,9 +95,16 @@ int b200q_model_create(const b200q_model_config* cfg, b200q_model_t* out) {
   return B200Q_OK;
 }
 
+int64_t b200q_model_workspace_bytes_of(b200q_model_t m) {
+  if (!m) return -1;
+  return m->lay ? layered_workspace_bytes(m) : b200q_model_workspace_bytes(&m->cfg);
+}
+
 int b200q_model_destroy(b200q_model_t m) {
-  if (m)
+  if (m) {
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
+    layered_destroy(m);
+  }
   delete m;
   return B200Q_OK;
 }
@@ -142,6 +113,7 @@ int b200q_model_bind_weight(b200q_model_t m, const char* name, const void* p, in
                             int64_t cols) {
   B200Q_CHECK_ARG(m && name && p, "bind_weight: null argument");
   B200Q_CHECK_ARG((reinterpret_cast<uintptr_t>(p) & 15) == 0, "weight %s not 16-byte aligned", name);
+  if (m->lay) return layered_bind_weight(m, name, p, rows, cols);
   const b200q_model_config& c = m->cfg;
   const int64_t H = c.hidden, I = c.intermediate, QKV = qkv_dim(c),
                 QD = (int64_t)c.n_q_heads * c.head_dim;
@@ -201,6 +173,7 @@ int b200q_model_bind_rope(b200q_model_t m, const void* p) {
 
 int b200q_model_bind_workspace(b200q_model_t m, void* p, int64_t bytes) {
   B200Q_CHECK_ARG(m && p, "bind_workspace: bad argument");
+  if (m->lay) return layered_bind_workspace(m, p, bytes);
   const b200q_model_config& c = m->cfg;
   const int64_t need = b200q_model_workspace_bytes(&c);
   B200Q_CHECK_ARG(bytes >= need, "workspace too small: %lld < %lld", (long long)bytes,
@@ -256,6 +229,7 @@ int b200q_model_profile_collect(b200q_model_t m, b200q_profile* out, int reset) 
 
 int b200q_model_forward(b200q_model_t m, const b200q_batch* b, void* stream) {
   B200Q_CHECK_ARG(m && b, "forward: null argument");
+  if (m->lay) return layered_forward(m, b, stream);
   const b200q_model_config& c = m->cfg;
   if (!m->embed || !m->final_norm || !m->lm_head || !m->kv || !m->rope || !m->ws) {
     set_error("forward: model not fully bound (embed/final_norm/lm_head/kv/rope/workspace)");
@@ -404,6 +378,7 @@ int b200q_model_forward(b200q_model_t m, const b200q_batch* b, void* stream) {
 // accessors for engine.cu
 namespace b200q {
 const b200q_model_config& model_cfg(b200q_model_t m) { return m->cfg; }
+const float* model_logits_f32(b200q_model_t m) { return m && m->lay ? m->lay->logits : nullptr; }
 int64_t model_num_blocks(b200q_model_t m) { return m->num_blocks; }
 bool model_is_profiling(b200q_model_t m) { return m->profiling; }
 }  // namespace b200q

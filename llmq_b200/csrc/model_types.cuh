@@ -1,0 +1,96 @@
+// model_types.cuh — the model object behind b200q_model_t, shared by model.cu (llama / gemma2 forward)
+// and layered.cu (layered architectures).
+#pragma once
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+using b200q::bf16;
+
+// one layer of a layered architecture: its description, bound weights and where its cache / state live
+struct b200q_layered_layer {
+  b200q_layer_desc d{};
+  const float *norm1 = nullptr, *norm2 = nullptr;
+  // latent attention
+  const void *down = nullptr, *uq = nullptr, *uk_t = nullptr, *uv = nullptr;
+  const float *q_norm = nullptr, *kv_norm = nullptr;
+  // general delta
+  const void *proj = nullptr, *w2 = nullptr;
+  const float *w0 = nullptr, *a_bias = nullptr, *out_norm = nullptr;
+  const void* o = nullptr;  // output projection of either mixer
+  // feed-forward
+  const void *up = nullptr, *ff_down = nullptr;
+  const float* act = nullptr;
+  const void* router = nullptr;
+  const float* router_bias = nullptr;
+  const void *experts_gate_up = nullptr, *experts_down = nullptr, *shared_gate_up = nullptr,
+             *shared_down = nullptr, *shared_gate = nullptr;
+  int64_t cache_block_off = 0;  // bytes per block of the cache regions before this layer's (own cache only)
+  int64_t state_off = 0;        // floats into a state slot
+  double* freq = nullptr;       // device, [rot_dims/2]
+};
+
+struct b200q_layered {
+  std::vector<b200q_layered_layer> layers;
+  int64_t kv_block_bytes = 0;
+  int64_t state_slot_floats = 0;
+  float* state = nullptr;
+  int64_t n_slots = 0;
+  float* tap = nullptr;
+  // workspace views (element type = cfg.dtype unless float)
+  float *x = nullptr, *qa = nullptr, *rlog = nullptr, *wts = nullptr, *sgate = nullptr, *logits = nullptr;
+  void *h1 = nullptr, *h2 = nullptr, *mix = nullptr, *ffo = nullptr, *proj = nullptr, *cq = nullptr, *q = nullptr,
+       *olat = nullptr, *attn = nullptr, *ffh = nullptr, *ffa = nullptr, *egu = nullptr, *eact = nullptr,
+       *eout = nullptr, *shout = nullptr, *sel = nullptr, *logits_bf16 = nullptr;
+  int32_t *idx = nullptr, *group_off = nullptr, *perm_tok = nullptr, *pair_pos = nullptr;
+};
+
+struct b200q_layer {
+  const void* input_norm = nullptr;
+  const void* qkv = nullptr;
+  const void* o = nullptr;
+  const void* post_norm = nullptr;  // llama: post_attention_layernorm (= the pre-MLP norm)
+  const void* gate_up = nullptr;
+  const void* down = nullptr;
+  // gemma2: the sandwich norms
+  const void* post_attn_norm = nullptr;
+  const void* pre_ffn_norm = nullptr;
+  const void* post_ffn_norm = nullptr;
+};
+
+struct b200q_model {
+  b200q_model_config cfg;
+  const void* embed = nullptr;
+  const void* final_norm = nullptr;
+  const void* lm_head = nullptr;
+  std::vector<b200q_layer> layers;
+  uint8_t* kv = nullptr;
+  int64_t num_blocks = 0;
+  const void* rope = nullptr;
+  // workspace views
+  uint8_t* ws = nullptr;
+  int64_t ws_bytes = 0;
+  // (no [T, 2I] gate_up buffer: the SwiGLU is applied in the gate_up GEMM's epilogue)
+  bf16 *x = nullptr, *residual = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr,
+       *sel = nullptr, *logits = nullptr;
+  // fold the split-K reduce of decode-sized projections into the consuming kernel (B200Q_FUSE_SPLITK=0: off)
+  bool fuse_splitk = true;
+  b200q_layered* lay = nullptr;  // B200Q_ARCH_RAMOPEL: everything layer-specific lives here
+  // optional per-category device timing (CUDA events on the forward's stream)
+  bool profiling = false;
+  std::vector<cudaEvent_t> ev_pool;
+  struct Span { int cat; double work; int e0, e1; };
+  std::vector<Span> spans;
+  int ev_used = 0;
+  b200q_profile prof{};
+  int get_event() {
+    if (ev_used == (int)ev_pool.size()) {
+      cudaEvent_t e;
+      cudaEventCreate(&e);
+      ev_pool.push_back(e);
+    }
+    return ev_used++;
+  }
+};
+

@@ -45,11 +45,33 @@ class ModelConfig(C.Structure):
         ("attn_softcap", C.c_float),
         ("final_softcap", C.c_float),
         ("embed_scale", C.c_float),
+        # layered architectures
+        ("dtype", C.c_int32),
+        ("max_logit_rows", C.c_int32),
+        ("state_slots", C.c_int32),
     ]
 
 
 ARCH_LLAMA = 0
 ARCH_GEMMA2 = 1
+ARCH_RAMOPEL = 2
+DTYPE_BF16 = 0
+DTYPE_F32 = 1
+MIXER_LATENT_ATTN = 1
+MIXER_GENERAL_DELTA = 2
+FF_NONE = 0
+FF_POLYNORM = 1
+FF_MOE = 2
+
+
+class LayerDesc(C.Structure):
+    _fields_ = [
+        ("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("rot_dim", C.c_int32),
+        ("vdim", C.c_int32), ("q_rank", C.c_int32), ("kv_rank", C.c_int32), ("kv_from", C.c_int32),
+        ("window", C.c_int32), ("rot_dims", C.c_int32), ("rot_base", C.c_double), ("attn_scale", C.c_float),
+        ("decay_rank", C.c_int32), ("ff", C.c_int32), ("ff_dim", C.c_int32), ("n_experts", C.c_int32),
+        ("top_k", C.c_int32), ("expert_limit", C.c_float), ("shared_dim", C.c_int32), ("shared_limit", C.c_float),
+    ]
 
 
 class Batch(C.Structure):
@@ -71,6 +93,10 @@ class Batch(C.Structure):
         ("sum_ctx_dec", C.c_int64),
         ("prefill_flops_per_layer", C.c_int64),
         ("prev_out_ids", C.c_void_p),
+        ("n_rows", C.c_int32),
+        ("seq_desc", C.c_void_p),
+        ("row_seq", C.c_void_p),
+        ("no_sampling", C.c_int32),
     ]
 
 
@@ -112,7 +138,7 @@ FLAG_FINISHED_EOS = 1
 FLAG_FINISHED_LENGTH = 2
 FLAG_FINISHED_ABORT = 4
 
-_vp, _i, _f, _i64 = C.c_void_p, C.c_int, C.c_float, C.c_int64
+_vp, _i, _f, _i64, _ll = C.c_void_p, C.c_int, C.c_float, C.c_int64, C.c_longlong
 
 # name -> (restype, argtypes); must list every symbol include/b200q.h declares
 SIGNATURES = {
@@ -143,6 +169,31 @@ SIGNATURES = {
     "b200q_prefill_attn_ex": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _f, _i, _vp]),
     "b200q_gemm_geglu_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "b200q_softcap_bf16": (_i, [_vp, _i64, _f, _vp]),
+    # layered architectures
+    "b200q_embed_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "b200q_centered_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "b200q_linear": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200q_linear_batched": (_i, [_vp, _i, _ll, _vp, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _i, _vp]),
+    "b200q_linear_grouped": (_i, [_vp, _i, _vp, _vp, _ll, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b200q_latent_prep": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "b200q_rope_pairs_q": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200q_latent_attn": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _vp]),
+    "b200q_delta_rule": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp]),
+    "b200q_polynorm": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "b200q_clamped_glu": (_i, [_vp, _vp, _i64, _i, _f, _i, _vp]),
+    "b200q_moe_route": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_layer_sum": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "b200q_argmax_f32": (_i, [_vp, _vp, _i, _i, _vp]),
+    "b200q_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
+    "b200q_copy_f32": (_i, [_vp, _vp, _i64, _vp]),
+    "b200q_model_create_layered": (_i, [C.POINTER(ModelConfig), C.POINTER(LayerDesc), C.POINTER(_vp)]),
+    "b200q_model_kv_block_bytes": (_i64, [_vp]),
+    "b200q_model_state_slot_bytes": (_i64, [_vp]),
+    "b200q_model_bind_state": (_i, [_vp, _vp, _i64]),
+    "b200q_model_logits_f32_ptr": (_vp, [_vp]),
+    "b200q_model_set_layer_tap": (_i, [_vp, _vp]),
+    "b200q_model_workspace_bytes_of": (_i64, [_vp]),
+    "b200q_engine_step_replay": (_i, [_vp, C.c_int32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_model_create": (_i, [C.POINTER(ModelConfig), C.POINTER(_vp)]),
     "b200q_model_destroy": (_i, [_vp]),
     "b200q_model_bind_weight": (_i, [_vp, C.c_char_p, _vp, _i64, _i64]),
@@ -198,6 +249,32 @@ def load() -> C.CDLL:
         fn.argtypes = args
     _lib = lib
     return lib
+
+
+def ensure_built() -> None:
+    """Build libb200q.so in-tree if it is missing or older than its sources (a fresh checkout holds no
+    built files).  One builder at a time: concurrent callers wait on a lock file beside the sources."""
+    import fcntl
+    import subprocess
+
+    csrc = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
+    inc = os.path.join(os.path.dirname(csrc), os.pardir, "include", "b200q.h")
+    srcs = [os.path.join(csrc, f) for f in os.listdir(csrc) if f.endswith((".cu", ".cuh")) or f == "Makefile"] + [inc]
+
+    def fresh() -> bool:
+        return os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= max(os.path.getmtime(f) for f in srcs)
+
+    if fresh():
+        return
+    with open(os.path.join(csrc, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not fresh():
+            env = dict(os.environ)
+            env["PATH"] = env.get("PATH", "") + os.pathsep + "/usr/local/cuda/bin"
+            r = subprocess.run(["make", "-C", csrc, f"-j{min(os.cpu_count() or 4, 16)}"], env=env,
+                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            if r.returncode != 0:
+                raise ImportError(f"building {LIB_PATH} failed:\n{r.stdout[-4000:]}")
 
 
 def check(rc: int) -> None:

@@ -17,6 +17,7 @@ from typing import Dict, Iterable, List, Optional, Tuple
 import torch
 
 from . import lib as L
+from . import ramopel
 
 BLOCK_SIZE = 16
 
@@ -187,7 +188,7 @@ GEMMA_2_2B = ModelSpec(hidden=2304, n_layers=26, n_q_heads=8, n_kv_heads=4, head
                        bos_token_id=2, name="gemma-2-2b", arch="gemma2", query_pre_attn_scalar=256.0,
                        attn_softcap=50.0, final_softcap=30.0, sliding_window=4096)
 BUILTIN_SPECS = {"llama-3-8b": LLAMA_3_8B, "llama-3.2-1b": LLAMA_32_1B,
-                 "gemma-2-9b": GEMMA_2_9B, "gemma-2-2b": GEMMA_2_2B}
+                 "gemma-2-9b": GEMMA_2_9B, "gemma-2-2b": GEMMA_2_2B, **ramopel.BUILTIN_SPECS}
 
 
 def rope_table(max_pos: int, head_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
@@ -296,7 +297,26 @@ def resolve_model(model_name: str) -> Tuple[ModelSpec, Optional[str]]:
         raise FileNotFoundError(f"{cfg_path} not found: pass a local model directory (offline deployment)")
     with open(cfg_path) as f:
         cfg = json.load(f)
-    return ModelSpec.from_hf_config(cfg, name=os.path.basename(os.path.normpath(model_name))), model_name
+    name = os.path.basename(os.path.normpath(model_name))
+    if cfg.get("architecture") == ramopel.ARCHITECTURE:
+        ckpt = os.path.join(model_name, "model.safetensors")
+        shapes = ramopel.checkpoint_shapes(ckpt) if os.path.exists(ckpt) else None
+        return ramopel.RamopelSpec.from_config(cfg, shapes, name=name), model_name
+    return ModelSpec.from_hf_config(cfg, name=name), model_name
+
+
+def checkpoint_engine_weights(spec, model_dir: str) -> Iterable[Tuple[str, torch.Tensor]]:
+    """the engine-layout weights of the checkpoint in `model_dir`, for whatever architecture `spec` is"""
+    if getattr(spec, "layered", False):
+        return ramopel.engine_weights(spec, ramopel.load_checkpoint(os.path.join(model_dir, "model.safetensors")))
+    return fuse_hf_weights(spec, load_hf_state_dict(model_dir))
+
+
+def random_weights(spec, seed: int, device) -> Iterable[Tuple[str, torch.Tensor]]:
+    """random-init engine-layout weights for whatever architecture `spec` is (benchmarks)"""
+    if getattr(spec, "layered", False):
+        return ramopel.engine_weights(spec, ramopel.random_checkpoint(spec, seed, device))
+    return random_engine_weights(spec, seed, device)
 
 
 class NativeModel:
@@ -306,12 +326,24 @@ class NativeModel:
     def __init__(self, spec: ModelSpec, weights: Iterable[Tuple[str, torch.Tensor]], *,
                  max_tokens: int = 4096, max_seqs: int = 256, max_model_len: int = 2048,
                  num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.9,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16,
+                 max_logit_rows: int = 0):
+        """dtype: element type of matrices, activations and cache — bfloat16, or float32 for the layered
+        architectures (true fp32 everywhere).  max_logit_rows: rows of the fp32 logits buffer a replayed
+        step may ask for (layered architectures; 0 = max_seqs)."""
         L.require_device()
         self.spec = spec
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.lib = L.load()
         self.max_model_len = min(max_model_len, spec.max_position_embeddings)
+        self.dtype = dtype
+        self.layered = bool(getattr(spec, "layered", False))
+        self.state = None
+        if self.layered:
+            self._init_layered(weights, max_tokens, max_seqs, num_blocks, gpu_memory_utilization, max_logit_rows)
+            return
+        if dtype != torch.bfloat16:
+            raise ValueError(f"{spec.arch}: only bfloat16 is implemented (float32 runs on the layered architectures)")
         if spec.arch != "gemma2" and spec.sliding_window:
             # Mistral-style window on every layer: not implemented as a window — the context is
             # capped to it instead, so the window never bites and results stay exact
@@ -358,6 +390,68 @@ class NativeModel:
         L.check(self.lib.b200q_model_bind_kv(h, self.kv.data_ptr(), self.num_blocks))
         torch.cuda.synchronize(self.device)
 
+    def _init_layered(self, weights, max_tokens, max_seqs, num_blocks, gpu_memory_utilization, max_logit_rows):
+        """a layered architecture (Ramopel): one b200q_layer_desc per layer, a paged cache of latents for the
+        attention layers that own one, and one fp32 recurrent-state slot per live sequence"""
+        spec, lib = self.spec, self.lib
+        if self.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {self.dtype} unsupported: bfloat16 or float32")
+        f32 = self.dtype == torch.float32
+        self.cfg = L.ModelConfig(
+            hidden=spec.hidden, n_layers=spec.n_layers, vocab=spec.vocab, block_size=BLOCK_SIZE,
+            max_tokens=max_tokens, max_seqs=max_seqs, max_pos=self.max_model_len, rms_eps=spec.rms_eps,
+            arch=L.ARCH_RAMOPEL, embed_scale=spec.embed_scale, dtype=L.DTYPE_F32 if f32 else L.DTYPE_BF16,
+            max_logit_rows=max_logit_rows, state_slots=max_seqs)
+        descs = (L.LayerDesc * spec.n_layers)(*[ly.desc() for ly in spec.layers])
+        h = C.c_void_p()
+        L.check(lib.b200q_model_create_layered(C.byref(self.cfg), descs, C.byref(h)))
+        self.handle = h
+        self._keep: List[torch.Tensor] = []
+        for name, t in weights:
+            # 2-D: a matrix, in the model's dtype; 1-D: a vector or constants, as one fp32 row
+            if t.dim() == 2:
+                t = t.to(device=self.device, dtype=self.dtype).contiguous()
+            else:
+                t = t.reshape(1, -1).to(device=self.device, dtype=torch.float32).contiguous()
+            self._keep.append(t)
+            L.check(lib.b200q_model_bind_weight(h, name.encode(), t.data_ptr(), t.shape[0], t.shape[1]))
+        ws_bytes = int(lib.b200q_model_workspace_bytes_of(h))
+        if ws_bytes <= 0:
+            raise L.B200QError(ws_bytes, "workspace sizing failed")
+        self.workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
+        L.check(lib.b200q_model_bind_workspace(h, self.workspace.data_ptr(), ws_bytes))
+        slot_bytes = int(lib.b200q_model_state_slot_bytes(h))
+        if slot_bytes > 0:
+            self.state = torch.zeros(max_seqs * slot_bytes // 4, dtype=torch.float32, device=self.device)
+            L.check(lib.b200q_model_bind_state(h, self.state.data_ptr(), max_seqs))
+        block_bytes = int(lib.b200q_model_kv_block_bytes(h))
+        if num_blocks is None:
+            # a model without attention layers still schedules by blocks: bound them by the context limit
+            num_blocks = (self.pool_blocks_for(gpu_memory_utilization, block_bytes) if block_bytes > 0
+                          else max_seqs * ((self.max_model_len + BLOCK_SIZE - 1) // BLOCK_SIZE))
+        if num_blocks < 1:
+            raise MemoryError(f"cache pool of {num_blocks} blocks: gpu_memory_utilization={gpu_memory_utilization} "
+                              "leaves no room after weights, workspace and recurrent state")
+        if num_blocks * BLOCK_SIZE < self.max_model_len:
+            self.max_model_len = int(num_blocks) * BLOCK_SIZE
+        self.num_blocks = int(num_blocks)
+        self.kv = torch.zeros(max(self.num_blocks * block_bytes, 256), dtype=torch.uint8, device=self.device)
+        L.check(lib.b200q_model_bind_kv(h, self.kv.data_ptr(), self.num_blocks))
+        self.rope = None
+        torch.cuda.synchronize(self.device)
+
+    def logits_f32_view(self, n: int) -> torch.Tensor:
+        """fp32 [n, vocab] view of the logits the last forward of a layered model wrote"""
+        ptr = self.lib.b200q_model_logits_f32_ptr(self.handle)
+        off = ptr - self.workspace.data_ptr()
+        return self.workspace[off: off + n * self.spec.vocab * 4].view(torch.float32).view(n, self.spec.vocab)
+
+    def set_layer_tap(self, buf: Optional[torch.Tensor]) -> None:
+        """layered models: the next forwards copy the fp32 residual stream after every layer into `buf`
+        ([n_layers, T, width]); None switches it off"""
+        self._tap = buf
+        L.check(self.lib.b200q_model_set_layer_tap(self.handle, buf.data_ptr() if buf is not None else None))
+
     def pool_blocks_for(self, gpu_memory_utilization: float, block_bytes: int) -> int:
         """KV blocks that fit `gpu_memory_utilization` of the device — vLLM's meaning of the knob
         (ref:llmq/workers/vllm_worker.py:107): the worker may use that fraction of the device; what
@@ -395,7 +489,7 @@ class NativeModel:
             self.lib.b200q_model_destroy(self.handle)
             self.handle = None
             self._keep.clear()
-            self.kv = self.workspace = self.rope = None
+            self.kv = self.workspace = self.rope = self.state = None
             torch.cuda.empty_cache()
 
 
@@ -461,6 +555,26 @@ class Engine:
                                            self._flg.ctypes.data, self.cap, C.byref(n)))
         k = n.value
         return self._ids[:k], self._tok[:k], self._flg[:k]
+
+    def step_replay(self, entries):
+        """One step whose work the caller lays down (teacher forcing): `entries` is a list of
+        (req_id, tokens, want) — the request's next tokens and the places among them whose logits are
+        wanted.  All entries run as one batch through the engine's own step builder, cache and kernels; a
+        request is admitted at its first entry and lives until abort().  Returns fp32 [sum(len(want)), vocab]
+        in the order of the entries."""
+        np = self.np
+        ids = np.asarray([e[0] for e in entries], dtype=np.int64)
+        ntok = np.asarray([len(e[1]) for e in entries], dtype=np.int32)
+        toks = np.ascontiguousarray(np.concatenate([np.asarray(e[1], dtype=np.int32).reshape(-1) for e in entries]))
+        nwant = np.asarray([len(e[2]) for e in entries], dtype=np.int32)
+        want = np.ascontiguousarray(np.concatenate(
+            [np.asarray(e[2], dtype=np.int32).reshape(-1) for e in entries] + [np.zeros(1, dtype=np.int32)]))
+        out = np.empty((int(nwant.sum()), self.model.spec.vocab), dtype=np.float32)
+        buf = out if out.size else np.empty((1, 1), dtype=np.float32)
+        L.check(self.lib.b200q_engine_step_replay(self.handle, len(entries), ids.ctypes.data, ntok.ctypes.data,
+                                                  toks.ctypes.data, nwant.ctypes.data, want.ctypes.data,
+                                                  buf.ctypes.data))
+        return out
 
     @property
     def stream_ptr(self) -> int:

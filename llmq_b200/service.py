@@ -459,7 +459,7 @@ def build_service(model_name: str, *, max_num_seqs: Optional[int], max_model_len
     """model + KV pool + engine + tokenizer for `model_name` (local dir or random:<builtin>)."""
     import torch
 
-    from .model import Engine, NativeModel, fuse_hf_weights, load_hf_state_dict, random_engine_weights, resolve_model
+    from .model import Engine, NativeModel, checkpoint_engine_weights, random_weights, resolve_model
 
     L.require_device()  # raises: this worker has no CPU path
     spec, model_dir = resolve_model(model_name)
@@ -476,14 +476,20 @@ def build_service(model_name: str, *, max_num_seqs: Optional[int], max_model_len
     if model_dir is None:
         from .fixtures import build_tokenizer, special_token_ids
 
-        weights = random_engine_weights(spec, seed, device)
+        weights = random_weights(spec, seed, device)
         tokenizer = build_tokenizer(spec.vocab)
         stop_ids = [special_token_ids(spec.vocab)["<|end_of_text|>"]]
     else:
-        from transformers import AutoTokenizer
+        weights = checkpoint_engine_weights(spec, model_dir)
+        if any(os.path.exists(os.path.join(model_dir, f)) for f in ("tokenizer.json", "tokenizer_config.json",
+                                                                    "tokenizer.model")):
+            from transformers import AutoTokenizer
 
-        weights = fuse_hf_weights(spec, load_hf_state_dict(model_dir))
-        tokenizer = AutoTokenizer.from_pretrained(model_dir)
+            tokenizer = AutoTokenizer.from_pretrained(model_dir)
+        else:  # a bare checkpoint (config + weights): one word per id, so any id sequence can be written
+            from .fixtures import build_tokenizer
+
+            tokenizer = build_tokenizer(spec.vocab)
         stop_ids = collect_stop_ids(model_dir, spec, tokenizer)
     model = NativeModel(spec, weights, max_tokens=budget, max_seqs=max_num_seqs,
                         max_model_len=max_model_len, gpu_memory_utilization=gpu_memory_utilization,
