@@ -585,6 +585,151 @@ def run_native(args):
     model.close()
 
 
+# ------------------------------------------------------------------------------------------------
+# --compare ramopel: the Ramopel decoder beside a Llama decoder of equal size (same width, layer count
+# and matrix bytes per decoded token), random weights, prefill and decode throughput through the engine's
+# own scheduler, with the device time of every kernel category (CUDA events inside the forward).
+# ------------------------------------------------------------------------------------------------
+def llama_of_equal_size(rspec):
+    from llmq_b200.model import ModelSpec
+
+    H, Lr = rspec.width, rspec.n_layers
+    n_q, n_kv, D = max(H // 128, 1), max(min(8, H // 128), 1), 128
+    attn = H * (n_q + 2 * n_kv) * D + H * n_q * D
+    per_layer = (rspec.weight_bytes_per_token() // 2 - 2 * rspec.vocab * H) / Lr
+    inter = max(256, int(round((per_layer - attn) / (3 * H) / 256)) * 256)
+    return ModelSpec(hidden=H, n_layers=Lr, n_q_heads=n_q, n_kv_heads=n_kv, head_dim=D, intermediate=inter,
+                     vocab=rspec.vocab, rope_theta=10000.0, tie_embeddings=False, max_position_embeddings=8192,
+                     name=f"llama-like-{rspec.name}")
+
+
+def run_compare(args):
+    import numpy as np
+    import torch
+
+    from llmq_b200 import lib as L
+    from llmq_b200.model import BUILTIN_SPECS, Engine, NativeModel, random_weights
+
+    torch.cuda.set_device(0)
+    L.require_device()
+    peaks = load_peaks()
+    S_p, n_p = args.compare_prompt, args.compare_prompts          # prefill: n_p prompts of S_p tokens
+    B, C0, G = args.compare_batch, args.compare_context, args.steps * 8   # decode: B sequences, context C0, G steps
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")
+    rng = np.random.default_rng(0)
+
+    def measure(spec):
+        budget = max(S_p * min(n_p, 2), B)
+        max_len = max(S_p, C0 + G + args.warmup * 8) + 16
+        blocks = (max(n_p * S_p, B * max_len) + 15) // 16 + max(B, n_p)
+        model = NativeModel(spec, random_weights(spec, 1234, torch.device("cuda", 0)), max_tokens=budget,
+                            max_seqs=max(B, n_p), max_model_len=max_len, num_blocks=blocks)
+        eng = Engine(model, max_num_seqs=max(B, n_p), max_num_batched_tokens=budget, max_model_len=max_len)
+        out = {}
+
+        def drain():
+            n = 0
+            while eng.has_work():
+                n += len(eng.step()[0])
+            torch.cuda.synchronize()
+            return n
+
+        def prefill_once(rid0):
+            for i in range(n_p):
+                eng.add_request(rid0 + i, rng.integers(3, spec.vocab, S_p).tolist(), 1, ignore_eos=True)
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            drain()
+            return time.perf_counter() - t0
+
+        for w in range(max(args.warmup, 3)):
+            prefill_once(1000 * (w + 1))
+        model.set_profiling(True)
+        model.collect_profile(reset=True)
+        ts = [prefill_once(100000 + 1000 * k) for k in range(args.steps)]
+        prof = model.collect_profile(reset=True)
+        model.set_profiling(False)
+        out["prefill"] = {"tokens_per_s": round(n_p * S_p / min(ts), 1), "ms": round(min(ts) * 1e3, 3),
+                          "tokens": n_p * S_p,
+                          "kernel_ms_per_run": {k: round(v["ms"] / args.steps, 3) for k, v in prof.items()},
+                          "launches_per_run": int(sum(v["launches"] for v in prof.values()) / args.steps)}
+        # decode: B sequences at context C0; the prompts go in first, then G timed decode-only steps
+        for i in range(B):
+            eng.add_request(900000 + i, rng.integers(3, spec.vocab, C0).tolist(), G + args.warmup * 8 + 1,
+                            ignore_eos=True)
+        got = 0
+        while got < B * (1 + args.warmup * 8):          # prompts + warm-up decode steps (graphs are captured here)
+            got += len(eng.step()[0])
+        torch.cuda.synchronize()
+        steps0 = eng.stats().steps
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        n = drain()
+        dt = time.perf_counter() - t0
+        n_steps = eng.stats().steps - steps0
+        out["decode"] = {"tokens_per_s": round(n / dt, 1), "ms_per_step": round(dt / max(n_steps, 1) * 1e3, 4),
+                         "batch": B, "context": C0, "steps": int(n_steps)}
+        # the same decode steps once more, eagerly with events around every kernel category
+        for i in range(B):
+            eng.add_request(1900000 + i, rng.integers(3, spec.vocab, C0).tolist(), 9, ignore_eos=True)
+        got = 0
+        while got < B:
+            got += len(eng.step()[0])
+        torch.cuda.synchronize()
+        model.set_profiling(True)
+        model.collect_profile(reset=True)
+        steps0 = eng.stats().steps
+        drain()
+        n_prof = eng.stats().steps - steps0
+        prof = model.collect_profile(reset=True)
+        model.set_profiling(False)
+        out["decode"]["kernel_ms_per_step"] = {k: round(v["ms"] / max(n_prof, 1), 4) for k, v in prof.items()}
+        out["decode"]["launches_per_step"] = int(sum(v["launches"] for v in prof.values()) / max(n_prof, 1))
+        eng.close()
+        model.close()
+        return out
+
+    results = {}
+    for key in args.compare_sizes.split(","):
+        rspec = BUILTIN_SPECS[key]
+        lspec = llama_of_equal_size(rspec)
+        wb = rspec.weight_bytes_per_token()
+        r, l = measure(rspec), measure(lspec)
+        n_attn = sum(1 for ly in rspec.layers if ly.mixer == "latent_attention")
+        a0 = next(ly for ly in rspec.layers if ly.mixer == "latent_attention")
+        d0 = next(ly for ly in rspec.layers if ly.mixer == "general_delta")
+        n_delta = rspec.n_layers - n_attn
+        # algorithmic bytes of one decode step (what a roofline-perfect kernel would move)
+        cache_r = B * min(C0, a0.window or C0) * (a0.kv_rank + a0.rot_dim) * 2 * n_attn
+        state_r = B * d0.heads * d0.dim * d0.dim * 4 * 2 * n_delta
+        cache_l = B * C0 * 2 * lspec.n_kv_heads * lspec.head_dim * 2 * lspec.n_layers
+        rk, lk = r["decode"]["kernel_ms_per_step"], l["decode"]["kernel_ms_per_step"]
+        frac = lambda by, ms: round(by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3) if ms > 0 else None
+        roof = {
+            "decode_weights": {"ramopel": frac(wb, rk["gemm"]), "llama": frac(lspec.weight_bytes_per_step(), lk["gemm"]),
+                               "unit": "fraction of measured HBM copy bandwidth, matrix bytes / gemm time"},
+            "decode_attention": {"ramopel_latent": frac(cache_r, rk["decode_attn"]),
+                                 "llama": frac(cache_l, lk["decode_attn"]),
+                                 "unit": "fraction of measured HBM copy bandwidth, cache bytes / attention time"},
+            "decode_recurrence": {"ramopel_delta": frac(state_r, rk["prefill_attn"]),
+                                  "unit": "fraction of measured HBM copy bandwidth, state bytes read+written / time"},
+        }
+        pf = 2.0 * (wb / 2 - rspec.vocab * rspec.width) * n_p * S_p       # matrix flops of the prefill (no lm head)
+        pfl = 2.0 * (lspec.weight_bytes_per_step() / 2 - 2 * lspec.vocab * lspec.hidden) * n_p * S_p
+        tf = lambda fl, ms: round(fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 3) if ms > 0 else None
+        roof["prefill_gemm"] = {"ramopel": tf(pf, r["prefill"]["kernel_ms_per_run"]["gemm"]),
+                                "llama": tf(pfl, l["prefill"]["kernel_ms_per_run"]["gemm"]),
+                                "unit": "fraction of measured cuBLAS bf16 throughput, matrix flops / gemm time"}
+        results[key] = {"ramopel": r, "llama_equal_size": {"intermediate": lspec.intermediate, **l},
+                        "matrix_gb_per_token": round(wb / 1e9, 3), "roofline": roof}
+    print(json.dumps({"compare": "ramopel", "dtype": "bf16", "data": "synthetic (random weights, random ids)",
+                      "peaks": peaks, "workload": {"prefill": f"{n_p} prompts x {S_p} tokens",
+                                                   "decode": f"{B} sequences at context {C0}"},
+                      "results": results}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -609,7 +754,18 @@ def main():
     ap.add_argument("--cpu-budget-s", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dry-run", action="store_true", help="host-logic self-test without a GPU (not a measurement)")
+    ap.add_argument("--compare", default=None, choices=["ramopel"],
+                    help="instead of the headline workload: prefill / decode throughput of this design beside a Llama "
+                         "decoder of equal size (random weights), one JSON line")
+    ap.add_argument("--compare-sizes", default="ramopel-1b,ramopel-3b")
+    ap.add_argument("--compare-prompt", type=int, default=2048)
+    ap.add_argument("--compare-prompts", type=int, default=4)
+    ap.add_argument("--compare-batch", type=int, default=128)
+    ap.add_argument("--compare-context", type=int, default=1024)
     args = ap.parse_args()
+    if args.compare:
+        run_compare(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

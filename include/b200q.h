@@ -211,10 +211,24 @@ int b200q_linear_batched(const void* A_dev, int lda, long long a_bs, const void*
                          void* C_dev, int ldc, long long c_bs, int M, int N, int K, int batch, int dtype,
                          int out_f32, void* stream);
 /* the same per group g (expert): rows [group_off[g], group_off[g+1]) of C use W + g*w_gs and read row
- * a_rows[r] of A (a_rows NULL: row r); max_rows bounds a group's rows */
+ * a_rows[r] of A (a_rows NULL: row r); max_rows bounds a group's rows.  With the tile table of
+ * b200q_moe_route (tile_tab / n_tiles, may be NULL), a_rows NULL and bf16 shapes the tensor-core form takes,
+ * the groups run on b200q_gemm_grouped_bf16. */
 int b200q_linear_grouped(const void* A_dev, int lda, const int32_t* a_rows_dev, const void* W_dev,
                          long long w_gs, void* C_dev, int ldc, const int32_t* group_off_dev, int groups,
-                         int max_rows, int N, int K, int dtype, void* stream);
+                         int max_rows, int N, int K, int dtype, const void* tile_tab_dev,
+                         const int32_t* n_tiles_dev, void* stream);
+/* the tensor-core form behind the batched and grouped linears (bf16 operands, fp32 accumulation; C bf16 or
+ * fp32):  C[row, g*c_gx + n] = sum_k A[row, g*a_gx + k] * W[g*N + n, k].  tab_dev != NULL: the m-tiles
+ * {group, first row, end row, 0} as b200q_moe_route wrote them (n_mt_dev of them, at most max_mtiles);
+ * tab_dev == NULL: `groups` groups of rows [0, M).  A is [a_rows, lda].  b200q_gemm_grouped_ok says whether
+ * the shapes are taken (K, N multiples of 64; operands and slices 16-byte aligned). */
+int b200q_gemm_grouped_bf16(const void* A_dev, long long a_rows, long long lda, int a_gx, const void* W_dev,
+                            int groups, void* C_dev, long long ldc, int c_gx, int M, int N, int K,
+                            const void* tab_dev, const int32_t* n_mt_dev, int max_mtiles, int out_f32,
+                            void* stream);
+int b200q_gemm_grouped_ok(const void* A_dev, long long lda, int a_gx, const void* W_dev, const void* C_dev,
+                          long long ldc, int c_gx, int N, int K, int out_f32);
 /* latent attention 1/3: proj row = [query latent | kv latent | shared rotated key part];
  *     cq = rmsnorm(query latent) * w_qn;  cache row slot_mapping[t] = [rmsnorm(kv latent) * w_kvn |
  *     rotate(key part)], pairs (2i, 2i+1) of the first rot_dims entries turned by position * freq[i]
@@ -252,9 +266,12 @@ int b200q_clamped_glu(const void* gate_up_dev, void* y_dev, int64_t rows, int F,
                       void* stream);
 /* top-k routing over fp32 router logits [T, E]: idx/wts [T, top] (softmax over the chosen logits), and the
  *     grouping of the T*top (token, choice) pairs by expert: group_off [E+1], perm_tok [T*top] (token of the
- *     pair at each sorted position), pair_pos [T*top] (sorted position of pair t*top+k) */
+ *     pair at each sorted position), pair_pos [T*top] (sorted position of pair t*top+k); optionally (NULL: not
+ *     written) the 128-row tiles of the groups for b200q_gemm_grouped_bf16: tile_tab [(T*top)/128 + E][4] =
+ *     {expert, first sorted row, end row of the expert, 0} and their count n_tiles [1] */
 int b200q_moe_route(const float* logits_dev, int T, int E, int top, int32_t* idx_dev, float* wts_dev,
-                    int32_t* group_off_dev, int32_t* perm_tok_dev, int32_t* pair_pos_dev, void* stream);
+                    int32_t* group_off_dev, int32_t* perm_tok_dev, int32_t* pair_pos_dev, int32_t* tile_tab_dev,
+                    int32_t* n_tiles_dev, void* stream);
 /* end of a parallel layer: x += mix + ff; ff = f (dense) or sum_k wts[t,k] expert_out[pair_pos[t*top+k]]
  *     (+ sigmoid(shared_gate[t]) shared_out[t]); unused parts NULL */
 int b200q_layer_sum(float* x_dev, const void* mix_dev, const void* f_dev, const void* expert_out_dev,

@@ -934,13 +934,14 @@ int b200q_engine_step_replay(b200q_engine_t e, int32_t n_entries, const int64_t*
     set_error("step_replay: more than max_num_seqs=%d live requests", e->cfg.max_num_seqs);
     return B200Q_ENOMEM;
   }
-  std::vector<Request*> sched;
+  std::vector<Request*> sched, fresh;
   int64_t to = 0, wo = 0;
   for (int i = 0; i < n_entries; ++i) {
     Request* r;
     auto it = e->by_id.find(req_ids[i]);
     if (it == e->by_id.end()) {
       r = new Request();
+      fresh.push_back(r);
       r->id = req_ids[i];
       r->n_prompt = 0;
       r->max_new = 0x3fffffff;
@@ -980,8 +981,16 @@ int b200q_engine_step_replay(b200q_engine_t e, int32_t n_entries, const int64_t*
       r->tokens.resize(r->tokens.size() - r->n_sched);
       r->n_prompt = (int32_t)r->tokens.size();
       r->n_sched = 0;
+      // pages taken for this step alone go back (the request keeps those of its computed tokens)
+      const size_t keep = (size_t)((r->n_computed + e->block_size - 1) / e->block_size);
+      while (r->blocks.size() > keep) {
+        e->free_blocks.push_back(r->blocks.back());
+        r->blocks.pop_back();
+      }
     }
   }
+  if (rc)  // a request admitted by a step that did not run was never live
+    for (Request* r : fresh) retire_request(e, r);
   return rc;
 }
 

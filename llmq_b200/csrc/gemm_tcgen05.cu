@@ -649,11 +649,13 @@ struct TmapKeyHash {
 };
 
 // bf16 row-major [rows, cols] -> tiled map with box {64 cols, box_rows rows}, 128B swizzle
+// (ld: elements between rows, 0 = dense)
 static int get_tmap(const void* ptr, long long rows, long long cols, int box_rows,
-                    CUtensorMap* out) {
+                    CUtensorMap* out, long long ld = 0) {
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   static std::mutex mu;
-  TmapKey key{ptr, rows, cols, box_rows};
+  if (ld == 0) ld = cols;
+  TmapKey key{ptr, rows, cols + (ld << 24), box_rows};
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
@@ -668,7 +670,7 @@ static int get_tmap(const void* ptr, long long rows, long long cols, int box_row
     return B200Q_ECUDA;
   }
   cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+  cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
@@ -901,6 +903,198 @@ static int choose_splits(int M, int N, int K, bool invariant, int forced_bn) {
 }
 int g_gemm_mode = 0;      // 0 = auto, 1 = force 1-CTA kernels, 2 = force the 2-CTA kernel
 
+
+// ------------------------------------------------------------------------------------------------
+// Grouped GEMM: many small GEMMs that share K and N run as ONE persistent launch — the experts of a
+// routed feed-forward (group = expert, rows = the (token, choice) pairs sorted by expert) or per-head
+// projections (group = head, every group has all rows and its own column slice of A and C).
+//   C[row, g*c_gx + n] = sum_k A[row, g*a_gx + k] * W[g*N + n, k]
+// Same pipeline as gemm_bf16_kernel (TMA producer warp, tcgen05.mma issuer warp, 4 epilogue warps, smem
+// ring, two TMEM accumulator stages); only the tile walk differs: m-tile i is {group, first row, end row}
+// read from a device table that the routing kernel wrote (tab != NULL, *n_mt entries), or computed
+// (tab == NULL: every group has ceil(M/128) m-tiles).  An A box always holds 128 rows: rows past a
+// group's end belong to the next group (or are zero-filled past the matrix) and their products are
+// never stored.  kOutF32: fp32 output (logits, latent-space queries) instead of bf16.
+// ------------------------------------------------------------------------------------------------
+struct GroupedArgs {
+  const int4* tab;     // [*n_mt] {group, row0, row_end, 0} or NULL
+  const int32_t* n_mt; // device count of m-tiles (tab != NULL)
+  int M, groups;       // tab == NULL: rows of every group, number of groups
+  int a_gx, c_gx;      // column offset per group in A / in C (elements)
+  long long ldc;
+};
+
+template <int BN, bool kOutF32>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        void* __restrict__ Cv, int N, int K, GroupedArgs ga) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint8_t* epi_smem = smem + STAGES * Cfg::STAGE_BYTES + 256;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt_per_group = (ga.M + GEMM_BM - 1) / GEMM_BM;
+  const int m_tiles = ga.tab ? *ga.n_mt : mt_per_group * ga.groups;
+  const int n_tiles = N / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = K / GEMM_BK;
+  auto tile_of = [&](int tile, int& g, int& row0, int& row_end, int& n_blk) {
+    const int mt = tile % m_tiles;
+    n_blk = tile / m_tiles;
+    if (ga.tab) {
+      const int4 e = ga.tab[mt];
+      g = e.x;
+      row0 = e.y;
+      row_end = e.z;
+    } else {
+      g = mt / mt_per_group;
+      row0 = (mt % mt_per_group) * GEMM_BM;
+      row_end = ga.M;
+    }
+  };
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(tmem_full + 0, 1);
+    mbar_init(tmem_full + 1, 1);
+    mbar_init(tmem_empty + 0, 4);
+    mbar_init(tmem_empty + 1, 4);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        int g, row0, row_end, n_blk;
+        tile_of(tile, g, row0, row_end, n_blk);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(empty + stage, phase ^ 1u);
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_expect_tx(full + stage, (uint32_t)(Cfg::A_BYTES + Cfg::B_BYTES));
+          tma_load_2d(sa, &tmap_a, g * ga.a_gx + kb * GEMM_BK, row0, full + stage);
+          tma_load_2d(sb, &tmap_b, kb * GEMM_BK, g * N + n_blk * BN, full + stage);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc = make_idesc(BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      mbar_wait(tmem_empty + acc, acc_phase ^ 1u);
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        mbar_wait(full + stage, phase);
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k)
+            umma_bf16(tmem_d, make_smem_desc(sa + k * 32), make_smem_desc(sb + k * 32), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty + stage);
+          if (kb == k_blocks - 1) umma_commit(tmem_full + acc);
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  } else {
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int g, row0, row_end, n_blk;
+      tile_of(tile, g, row0, row_end, n_blk);
+      mbar_wait(tmem_full + acc, acc_phase);
+      tc_fence_after();
+      const int r0 = row0 + quarter * 32;
+      const long long col0 = (long long)g * ga.c_gx + (long long)n_blk * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      if constexpr (kOutF32) {
+        const int row = r0 + lane;
+        float* crow = reinterpret_cast<float*>(Cv) + (long long)row * ga.ldc + col0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(taddr + (uint32_t)c0, v);
+          tmem_ld_wait();
+          if (row < row_end) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              st_v4(crow + c0 + 4 * j, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+          }
+        }
+      } else {
+        bf16* ctile = reinterpret_cast<bf16*>(Cv) + (long long)r0 * ga.ldc + col0;
+        epilogue_rows<BN, ACT_NONE>(taddr, ctile, ga.ldc, r0, row_end, epi_smem + (warp - 2) * EPI_SMEM_PER_WARP, lane);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty + acc);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int BN, bool kOutF32>
+static int launch_grouped(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int N, int K, const GroupedArgs& ga,
+                          int max_tiles, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_grouped_kernel<BN, kOutF32>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200Q_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_TOTAL));
+    attr_set = true;
+  }
+  const int grid = max_tiles < num_sms() ? max_tiles : num_sms();
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_TOTAL, st>>>(ta, tb, C, N, K, ga);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -945,6 +1139,44 @@ int b200q_stream_probe(const void* W, int N, int K, int rows, int stages, int mo
   stream_probe_kernel<<<grid, 64, smem_bytes, as_stream(stream)>>>(tm, (const uint8_t*)W, N, K, rows, stages, mode, sink);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
+}
+
+// Grouped / per-head GEMM on the tensor cores, see gemm_grouped_kernel.  Returns B200Q_EINVAL for shapes
+// it does not take (the caller falls back): K, N multiples of 64, 16-byte aligned operands and slices.
+int b200q_gemm_grouped_bf16(const void* A, long long a_rows, long long lda, int a_gx, const void* W, int groups,
+                            void* C, long long ldc, int c_gx, int M, int N, int K, const void* tab_dev,
+                            const int32_t* n_mt_dev, int max_mtiles, int out_f32, void* stream) {
+  B200Q_CHECK_ARG(A && W && C && groups > 0 && N > 0 && K > 0 && a_rows > 0, "gemm_grouped: bad argument");
+  B200Q_CHECK_ARG(b200q_gemm_grouped_ok(A, lda, a_gx, W, C, ldc, c_gx, N, K, out_f32),
+                  "gemm_grouped: unsupported shape N=%d K=%d lda=%lld ldc=%lld", N, K, lda, ldc);
+  B200Q_CHECK_ARG(tab_dev ? (n_mt_dev && max_mtiles > 0) : M >= 0, "gemm_grouped: bad tile description");
+  if (!tab_dev && M == 0) return B200Q_OK;
+  CUtensorMap ta, tb;
+  int rc = get_tmap(A, a_rows, lda, GEMM_BM, &ta);  // the whole matrix; a group's slice is a column offset
+  if (rc) return rc;
+  const int bn = N % 256 == 0 ? 256 : (N % 128 == 0 ? 128 : 64);
+  rc = get_tmap(W, (long long)groups * N, K, bn, &tb);
+  if (rc) return rc;
+  GroupedArgs ga{(const int4*)tab_dev, n_mt_dev, M, groups, a_gx, c_gx, ldc};
+  const long long mt = tab_dev ? max_mtiles : (long long)groups * ((M + GEMM_BM - 1) / GEMM_BM);
+  const long long tiles = mt * (N / bn);
+  const int cap = (int)(tiles < (1 << 30) ? tiles : (1 << 30));
+  cudaStream_t st = as_stream(stream);
+  if (out_f32) {
+    if (bn == 256) return launch_grouped<256, true>(ta, tb, C, N, K, ga, cap, st);
+    if (bn == 128) return launch_grouped<128, true>(ta, tb, C, N, K, ga, cap, st);
+    return launch_grouped<64, true>(ta, tb, C, N, K, ga, cap, st);
+  }
+  if (bn == 256) return launch_grouped<256, false>(ta, tb, C, N, K, ga, cap, st);
+  if (bn == 128) return launch_grouped<128, false>(ta, tb, C, N, K, ga, cap, st);
+  return launch_grouped<64, false>(ta, tb, C, N, K, ga, cap, st);
+}
+
+int b200q_gemm_grouped_ok(const void* A, long long lda, int a_gx, const void* W, const void* C, long long ldc,
+                          int c_gx, int N, int K, int out_f32) {
+  const int ca = out_f32 ? 4 : 8;  // elements of C per 16 bytes
+  return K % GEMM_BK == 0 && N % 64 == 0 && lda % 8 == 0 && a_gx % 8 == 0 && ldc % ca == 0 && c_gx % ca == 0 &&
+         ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C)) & 15) == 0;
 }
 
 // test/tuning hook (not part of the reference-facing surface): force the N tile (0 = auto)

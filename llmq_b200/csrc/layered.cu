@@ -35,9 +35,9 @@ int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
     const b200q_layer_desc& d = L[i];
     if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
       B200Q_CHECK_ARG(d.heads > 0 && d.dim >= 0 && d.rot_dim >= 0 && d.dim + d.rot_dim > 0 && d.vdim > 0 &&
-                          d.q_rank > 0 && d.kv_rank > 0 && d.kv_rank <= 512 && d.window >= 0 && d.rot_dims >= 0 &&
+                          d.q_rank > 0 && d.kv_rank > 0 && d.kv_rank <= 1024 && d.window >= 0 && d.rot_dims >= 0 &&
                           d.rot_dims % 2 == 0 && d.rot_dims <= d.rot_dim,
-                      "layer %d: bad latent attention sizes (kv_rank <= 512, even rot.dims <= rot_dim)", i);
+                      "layer %d: bad latent attention sizes (kv_rank <= 1024, even rot.dims <= rot_dim)", i);
       if (d.kv_from >= 0) {
         B200Q_CHECK_ARG(d.kv_from < i && L[d.kv_from].mixer == B200Q_MIXER_LATENT_ATTN && L[d.kv_from].kv_from < 0 &&
                             L[d.kv_from].kv_rank == d.kv_rank && L[d.kv_from].rot_dim == d.rot_dim,
@@ -136,6 +136,9 @@ int64_t layout(b200q_model* m, uint8_t* base) {
   y->perm_tok = (int32_t*)take(T * w.pairs * 4);
   y->pair_pos = (int32_t*)take(T * w.pairs * 4);
   y->group_off = (int32_t*)take((w.experts + 1) * 4);
+  y->tile_tab = (int32_t*)take((T * w.pairs / 128 + w.experts + 1) * 16);
+  y->n_tiles = (int32_t*)take(16);
+  y->esrc = take(w.moe ? T * w.pairs * W * es : 1);
   y->egu = take(T * w.egu * es);
   y->eact = take(T * w.eact * es);
   y->eout = take(w.moe ? T * w.pairs * W * es : 1);
@@ -402,14 +405,20 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
       const int E = d.n_experts, K = d.top_k, F = d.ff_dim, P = T * K;
       LIN(y->h2, W, l.router, l.router_bias, y->rlog, E, E, W, 1);
       TRY(EW, (double)T * E * 4,
-          b200q_moe_route(y->rlog, T, E, K, y->idx, y->wts, y->group_off, y->perm_tok, y->pair_pos, stream));
+          b200q_moe_route(y->rlog, T, E, K, y->idx, y->wts, y->group_off, y->perm_tok, y->pair_pos, y->tile_tab,
+                          y->n_tiles, stream));
+      // bf16: the pairs' inputs are gathered into expert order once, so that each expert's rows are one
+      // dense block the tensor-core GEMM can fetch by TMA; fp32 reads them through perm_tok
+      const bool sorted = dt == B200Q_DTYPE_BF16 && W % 8 == 0;
+      if (sorted) TRY(EW, 2.0 * P * W * es, b200q_gather_rows(y->h2, y->perm_tok, y->esrc, P, W, stream));
       TRY(B200Q_PROF_GEMM, 2.0 * P * 2.0 * F * W,
-          b200q_linear_grouped(y->h2, W, y->perm_tok, l.experts_gate_up, 2LL * F * W, y->egu, 2 * F, y->group_off, E, P,
-                               2 * F, W, dt, stream));
+          b200q_linear_grouped(sorted ? y->esrc : y->h2, W, sorted ? nullptr : y->perm_tok, l.experts_gate_up,
+                               2LL * F * W, y->egu, 2 * F, y->group_off, E, P, 2 * F, W, dt, y->tile_tab, y->n_tiles,
+                               stream));
       TRY(EW, 3.0 * P * F * es, b200q_clamped_glu(y->egu, y->eact, P, F, d.expert_limit, dt, stream));
       TRY(B200Q_PROF_GEMM, 2.0 * P * (double)F * W,
           b200q_linear_grouped(y->eact, F, nullptr, l.experts_down, (long long)W * F, y->eout, W, y->group_off, E, P, W,
-                               F, dt, stream));
+                               F, dt, y->tile_tab, y->n_tiles, stream));
       const bool sh = d.shared_dim > 0;
       if (sh) {
         const int FS = d.shared_dim;

@@ -266,10 +266,9 @@ __global__ void __launch_bounds__(128) rope_q_kernel(const T* __restrict__ q, in
 // heads); a chunk of 32 cached rows is staged in shared memory once and used by all 8 heads (warp =
 // head, lane = key for the scores, lane = output dims for the weighted sum); online softmax in fp32.
 // The chunks start at the window's first key, so the arithmetic of a token does not depend on how the
-// prompt was cut or batched.  kv_rank <= 32 * LATENT_ACC.
+// prompt was cut or batched.  kv_rank <= 32 * LATENT_ACC (the accumulator registers of a lane).
 // ------------------------------------------------------------------------------------------------
-constexpr int LATENT_ACC = 16;
-template <typename T>
+template <typename T, int LATENT_ACC>
 __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restrict__ qa,
                                                           const T* __restrict__ cache,
                                                           const int32_t* __restrict__ block_table, int bt_stride,
@@ -522,7 +521,9 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int32_t* __restrict__ idx, int P, int top, int E,
                                                         int32_t* __restrict__ group_off,
                                                         int32_t* __restrict__ perm_tok,
-                                                        int32_t* __restrict__ pair_pos) {
+                                                        int32_t* __restrict__ pair_pos,
+                                                        int32_t* __restrict__ tile_tab,
+                                                        int32_t* __restrict__ n_tiles) {
   extern __shared__ int32_t si[];  // counts[E] | offs[E+1] | cursor[E]
   int32_t* counts = si;
   int32_t* offs = si + E;
@@ -538,6 +539,18 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int32_t* __restric
       run += counts[e];
     }
     offs[E] = run;
+    if (tile_tab) {  // the 128-row tiles of every non-empty group, for the grouped tensor-core GEMM
+      int n = 0;
+      for (int e = 0; e < E; ++e)
+        for (int r = offs[e]; r < offs[e + 1]; r += 128) {
+          tile_tab[4 * n + 0] = e;
+          tile_tab[4 * n + 1] = r;
+          tile_tab[4 * n + 2] = offs[e + 1];
+          tile_tab[4 * n + 3] = 0;
+          ++n;
+        }
+      *n_tiles = n;
+    }
   }
   __syncthreads();
   for (int e = threadIdx.x; e <= E; e += blockDim.x) group_off[e] = offs[e];
@@ -683,6 +696,9 @@ int b200q_linear(const void* A, int lda, const void* W, const float* bias, void*
   if (dtype == B200Q_DTYPE_BF16 && !out_f32 && !bias && lda == K && ldc == N && K % 64 == 0 && N % 64 == 0 &&
       ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C)) & 15) == 0)
     return b200q_gemm_bf16(A, W, C, M, N, K, stream);
+  // fp32 results (logits) of bf16 operands: the same pipeline with an fp32 epilogue
+  if (dtype == B200Q_DTYPE_BF16 && out_f32 && !bias && b200q_gemm_grouped_ok(A, lda, 0, W, C, ldc, 0, N, K, 1))
+    return b200q_gemm_grouped_bf16(A, M, lda, 0, W, 1, C, ldc, 0, M, N, K, nullptr, nullptr, 0, 1, stream);
   LinearArgs a{A, W, C, bias, nullptr, nullptr, 0, 0, 0, lda, ldc, M, N, K};
   return launch_linear(a, (M + 63) / 64, 1, dtype, out_f32, stream);
 }
@@ -692,16 +708,25 @@ int b200q_linear_batched(const void* A, int lda, long long a_bs, const void* W, 
   B200Q_CHECK_ARG(A && W && C && M >= 0 && N > 0 && K > 0 && batch > 0 && is_dtype(dtype),
                   "linear_batched: bad argument");
   if (M == 0) return B200Q_OK;
+  // per-head weights stacked [batch*N, K], every head a column slice of A and of C: one grouped launch
+  if (dtype == B200Q_DTYPE_BF16 && w_bs == (long long)N * K && a_bs < (1 << 30) && c_bs < (1 << 30) &&
+      b200q_gemm_grouped_ok(A, lda, (int)a_bs, W, C, ldc, (int)c_bs, N, K, out_f32))
+    return b200q_gemm_grouped_bf16(A, M, lda, (int)a_bs, W, batch, C, ldc, (int)c_bs, M, N, K, nullptr, nullptr, 0,
+                                   out_f32, stream);
   LinearArgs a{A, W, C, nullptr, nullptr, nullptr, a_bs, w_bs, c_bs, lda, ldc, M, N, K};
   return launch_linear(a, (M + 63) / 64, batch, dtype, out_f32, stream);
 }
 
 int b200q_linear_grouped(const void* A, int lda, const int32_t* a_rows, const void* W, long long w_gs, void* C,
                          int ldc, const int32_t* group_off, int groups, int max_rows, int N, int K, int dtype,
-                         void* stream) {
+                         const void* tile_tab, const int32_t* n_tiles, void* stream) {
   B200Q_CHECK_ARG(A && W && C && group_off && groups > 0 && max_rows >= 0 && N > 0 && K > 0 && is_dtype(dtype),
                   "linear_grouped: bad argument");
   if (max_rows == 0) return B200Q_OK;
+  if (dtype == B200Q_DTYPE_BF16 && tile_tab && n_tiles && !a_rows && w_gs == (long long)N * K &&
+      b200q_gemm_grouped_ok(A, lda, 0, W, C, ldc, 0, N, K, 0))
+    return b200q_gemm_grouped_bf16(A, max_rows, lda, 0, W, groups, C, ldc, 0, 0, N, K, tile_tab, n_tiles,
+                                   max_rows / 128 + groups, 0, stream);
   LinearArgs a{A, W, C, nullptr, a_rows, group_off, 0, w_gs, 0, lda, ldc, max_rows, N, K};
   return launch_linear(a, (max_rows + 63) / 64, groups, dtype, 0, stream);
 }
@@ -741,24 +766,31 @@ int b200q_latent_attn(const float* qa, const void* cache, const int32_t* block_t
   B200Q_CHECK_ARG(qa && cache && block_table && row_seq && positions && out && heads > 0 && T_ >= 0 &&
                       block_size > 0 && window >= 0 && is_dtype(dtype),
                   "latent_attn: bad argument");
-  B200Q_CHECK_ARG(kv_rank > 0 && kv_rank <= 32 * LATENT_ACC, "latent_attn: kv_rank=%d unsupported (1..%d)", kv_rank,
-                  32 * LATENT_ACC);
+  B200Q_CHECK_ARG(kv_rank > 0 && kv_rank <= 1024, "latent_attn: kv_rank=%d unsupported (1..1024)", kv_rank);
   if (T_ == 0) return B200Q_OK;
   const int RP = kv_rank + rot_dim;
   const size_t smem = (size_t)(8 * RP + 32 * (RP + 1)) * sizeof(float);
   B200Q_CHECK_ARG(smem <= 227 * 1024, "latent_attn: kv_rank + rot_dim = %d does not fit shared memory", RP);
   dim3 grid(T_, (heads + 7) / 8);
-  if (dtype == B200Q_DTYPE_F32) {
-    B200Q_CUDA(cudaFuncSetAttribute(latent_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    latent_attn_kernel<float><<<grid, 256, smem, as_stream(stream)>>>(qa, (const float*)cache, block_table, bt_stride,
-                                                                      row_seq, positions, heads, kv_rank, rot_dim,
-                                                                      block_size, window, scale, (float*)out);
-  } else {
-    B200Q_CUDA(cudaFuncSetAttribute(latent_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    latent_attn_kernel<bf16><<<grid, 256, smem, as_stream(stream)>>>(qa, (const bf16*)cache, block_table, bt_stride,
-                                                                     row_seq, positions, heads, kv_rank, rot_dim,
-                                                                     block_size, window, scale, (bf16*)out);
-  }
+#define LATENT_LAUNCH(TT, ACC)                                                                                     \
+  do {                                                                                                             \
+    B200Q_CUDA(cudaFuncSetAttribute(latent_attn_kernel<TT, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                    (int)smem));                                                                   \
+    latent_attn_kernel<TT, ACC><<<grid, 256, smem, as_stream(stream)>>>(                                           \
+        qa, (const TT*)cache, block_table, bt_stride, row_seq, positions, heads, kv_rank, rot_dim, block_size,    \
+        window, scale, (TT*)out);                                                                                  \
+  } while (0)
+#define LATENT_BY_RANK(TT)                          \
+  do {                                              \
+    if (kv_rank <= 128) LATENT_LAUNCH(TT, 4);       \
+    else if (kv_rank <= 256) LATENT_LAUNCH(TT, 8);  \
+    else if (kv_rank <= 512) LATENT_LAUNCH(TT, 16); \
+    else LATENT_LAUNCH(TT, 32);                     \
+  } while (0)
+  if (dtype == B200Q_DTYPE_F32) LATENT_BY_RANK(float);
+  else LATENT_BY_RANK(bf16);
+#undef LATENT_BY_RANK
+#undef LATENT_LAUNCH
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -808,7 +840,8 @@ int b200q_clamped_glu(const void* gate_up, void* y, int64_t rows, int F, float l
 }
 
 int b200q_moe_route(const float* logits, int T_, int E, int top, int32_t* idx, float* wts, int32_t* group_off,
-                    int32_t* perm_tok, int32_t* pair_pos, void* stream) {
+                    int32_t* perm_tok, int32_t* pair_pos, int32_t* tile_tab, int32_t* n_tiles, void* stream) {
+  B200Q_CHECK_ARG(!tile_tab == !n_tiles, "moe_route: tile_tab and n_tiles go together");
   B200Q_CHECK_ARG(logits && idx && wts && group_off && perm_tok && pair_pos && T_ >= 0 && E > 0 && top > 0 &&
                       top <= 32 && top <= E && E <= 4096,
                   "moe_route: bad argument (E=%d top=%d)", E, top);
@@ -816,7 +849,8 @@ int b200q_moe_route(const float* logits, int T_, int E, int top, int32_t* idx, f
   moe_route_kernel<<<(T_ + 3) / 4, 128, 0, as_stream(stream)>>>(logits, T_, E, top, idx, wts);
   B200Q_LAUNCH_CHECK();
   moe_plan_kernel<<<1, 1024, (size_t)(3 * E + 1) * sizeof(int32_t), as_stream(stream)>>>(idx, T_ * top, top, E,
-                                                                                          group_off, perm_tok, pair_pos);
+                                                                                          group_off, perm_tok, pair_pos,
+                                                                                          tile_tab, n_tiles);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

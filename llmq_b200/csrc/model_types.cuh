@@ -43,7 +43,9 @@ struct b200q_layered {
   void *h1 = nullptr, *h2 = nullptr, *mix = nullptr, *ffo = nullptr, *proj = nullptr, *cq = nullptr, *q = nullptr,
        *olat = nullptr, *attn = nullptr, *ffh = nullptr, *ffa = nullptr, *egu = nullptr, *eact = nullptr,
        *eout = nullptr, *shout = nullptr, *sel = nullptr, *logits_bf16 = nullptr;
-  int32_t *idx = nullptr, *group_off = nullptr, *perm_tok = nullptr, *pair_pos = nullptr;
+  int32_t *idx = nullptr, *group_off = nullptr, *perm_tok = nullptr, *pair_pos = nullptr, *tile_tab = nullptr,
+          *n_tiles = nullptr;
+  void* esrc = nullptr;  // the routed pairs' inputs gathered into expert order (bf16 path)
 };
 
 struct b200q_layer {

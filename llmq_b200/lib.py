@@ -174,14 +174,16 @@ SIGNATURES = {
     "b200q_centered_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200q_linear": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200q_linear_batched": (_i, [_vp, _i, _ll, _vp, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _i, _vp]),
-    "b200q_linear_grouped": (_i, [_vp, _i, _vp, _vp, _ll, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp]),
+    "b200q_linear_grouped": (_i, [_vp, _i, _vp, _vp, _ll, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "b200q_gemm_grouped_bf16": (_i, [_vp, _ll, _ll, _i, _vp, _i, _vp, _ll, _i, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
+    "b200q_gemm_grouped_ok": (_i, [_vp, _ll, _i, _vp, _vp, _ll, _i, _i, _i, _i]),
     "b200q_latent_prep": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200q_rope_pairs_q": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b200q_latent_attn": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _vp]),
     "b200q_delta_rule": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp]),
     "b200q_polynorm": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200q_clamped_glu": (_i, [_vp, _vp, _i64, _i, _f, _i, _vp]),
-    "b200q_moe_route": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_moe_route": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b200q_layer_sum": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp]),
     "b200q_argmax_f32": (_i, [_vp, _vp, _i, _i, _vp]),
     "b200q_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),

@@ -67,7 +67,8 @@ def latent_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, mx: 
     s = (torch.einsum("ihd,jhd->hij", qn, kn) + torch.einsum("ihp,jp->hij", qr, kr)) * mx["scale"]
     i = torch.arange(T)[:, None]
     j = torch.arange(T)[None, :]
-    seen = (i - j >= 0) & (i - j < mx["mask"]["size"])
+    size = (mx.get("mask") or {}).get("size", 0)   # no mask entry: every earlier key is seen
+    seen = (i - j >= 0) & ((i - j < size) if size else (i - j >= 0))
     s = s.masked_fill(~seen[None], float("-inf"))
     p = torch.softmax(s, -1)
     o = torch.einsum("hij,jhv->ihv", p, v).reshape(T, H * V)
@@ -156,3 +157,37 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
             stream.append(x.clone())
     logits = centered_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(stream)) if keep_layers else logits
+
+
+def windowed_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, pos: torch.Tensor,
+                       window: int, scale: float) -> torch.Tensor:
+    """q [n, H, d] asked at positions pos [n]; keys [L, d], values [L, r] of one sequence (shared by the
+    heads).  Position p sees j with 0 <= p - j < window (window 0: every j <= p).  -> [n, H, r]"""
+    out = torch.zeros(q.shape[0], q.shape[1], values.shape[1], dtype=q.dtype)
+    for i in range(q.shape[0]):
+        p = int(pos[i])
+        lo = max(0, p - window + 1) if window > 0 else 0
+        s = torch.einsum("hd,jd->hj", q[i], keys[lo:p + 1]) * scale
+        out[i] = torch.softmax(s, -1) @ values[lo:p + 1]
+    return out
+
+
+def delta_rule_steps(r, k, v, w, a, S0=None):
+    """the recurrence alone, one head: r, k, v, w (decay), a (removal) [T, D]; S0 [D, D] or None (zero).
+    -> (o [T, D], S_T)"""
+    T, D = k.shape
+    S = torch.zeros(D, D, dtype=k.dtype) if S0 is None else S0.clone()
+    o = torch.zeros(T, D, dtype=k.dtype)
+    for t in range(T):
+        u = k[t] / torch.sqrt((k[t] * k[t]).sum() + 1e-6)
+        S = w[t][:, None] * S - (a[t] * u)[:, None] * (u @ S)[None, :] + k[t][:, None] * v[t][None, :]
+        o[t] = S.T @ r[t]
+    return o, S
+
+
+def greedy(cfg: dict, weights: Dict[str, torch.Tensor], prompt: List[int], n_new: int, dtype=torch.float64) -> List[int]:
+    """greedy continuation, every step recomputed from the tokens"""
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(forward(cfg, weights, toks, dtype)[-1].argmax()))
+    return toks[len(prompt):]
