@@ -8,6 +8,8 @@
 // decays and gates of the recurrence, angles — is fp32 (angles fp64) in both instantiations.
 // Nothing here depends on which other rows share the batch: every reduction runs in a fixed order
 // per row, so a token's result is the same alone, in a chunk or in a mixed batch.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace b200q {
@@ -167,6 +169,34 @@ __global__ void __launch_bounds__(256) linear_kernel(LinearArgs a) {
       const int n = n0 + tx * 4 + j;
       if (n < a.N) stf(Cm + (long long)m * a.ldc + n, acc[i][j] + (a.bias ? a.bias[n] : 0.f));
     }
+  }
+}
+
+// few outputs per row (a router, a gate): one warp per (row, 8 outputs), lanes stride over K — every SM
+// gets work even when the whole product has a handful of 64 x 64 tiles.  Lane partials are summed in a
+// fixed order, so a row's result does not depend on the batch.
+template <typename T, typename TC>
+__global__ void __launch_bounds__(256) skinny_linear_kernel(LinearArgs a) {
+  const long long wg = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, n_groups = (a.N + 7) / 8;
+  const long long m = wg / n_groups;
+  const int n0 = (int)(wg % n_groups) * 8;
+  if (m >= a.M) return;
+  const T* A = (const T*)a.A + m * a.lda;
+  const T* Wm = (const T*)a.W;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int k = lane; k < a.K; k += 32) {
+    const float av = ldf(A + k);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (n0 + j < a.N) acc[j] = fmaf(av, ldf(Wm + (long long)(n0 + j) * a.K + k), acc[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float v = warp_sum(acc[j]);
+    if (lane == 0 && n0 + j < a.N) stf((TC*)a.C + m * a.ldc + n0 + j, v + (a.bias ? a.bias[n0 + j] : 0.f));
   }
 }
 
@@ -341,6 +371,193 @@ __global__ void __launch_bounds__(256) latent_attn_kernel(const float* __restric
 }
 
 // ------------------------------------------------------------------------------------------------
+// latent attention on the tensor cores (bf16 cache).  One CTA (4 warps) per (token, group of 16 heads):
+// the 16 heads are the M rows of mma.sync.m16n8k16 tiles and share every cached row, so a row fetched once
+// serves 16 heads twice (as key [latent | rotated part] and as value [latent]).
+//   * the fp32 query (already in latent space, times the score scale) is split into bf16 hi + lo parts and
+//     both are multiplied with the keys: the scores keep ~16 bits of the query instead of 8;
+//   * cached rows arrive in chunks of 64 keys by cp.async into a double-buffered shared-memory tile (the
+//     next chunk loads while this one is multiplied); rows of a chunk past the token's position are zeros;
+//   * warp w scores keys [16w, 16w+16) of the chunk, the chunk's row maxima / sums and the bf16 weights are
+//     exchanged through shared memory, then warp w accumulates output dims [w R/4, (w+1) R/4) over all
+//     64 keys (values read from the same tile with ldmatrix.trans); online softmax state in fp32.
+// Chunks start at the first key of the token's window, so a token's arithmetic does not depend on how the
+// prompt was cut or batched.  Needs kv_rank % 64 == 0, (kv_rank + rot_dim) % 16 == 0, kv_rank <= 32 * NTW.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+constexpr int LATENT_CHUNK = 64, LATENT_PLD = LATENT_CHUNK + 8;
+template <int NTW>
+__global__ void __launch_bounds__(128) latent_attn_mma_kernel(const float* __restrict__ qa,
+                                                              const bf16* __restrict__ cache,
+                                                              const int32_t* __restrict__ block_table, int bt_stride,
+                                                              const int32_t* __restrict__ row_seq,
+                                                              const int32_t* __restrict__ positions, int heads, int R,
+                                                              int P, int block_size, int window, float scale,
+                                                              bf16* __restrict__ out) {
+  extern __shared__ __align__(16) uint8_t smraw[];
+  const int RP = R + P, LDS = RP + 8;
+  bf16* qhi = reinterpret_cast<bf16*>(smraw);             // [16][LDS]
+  bf16* qlo = qhi + 16 * LDS;                             // [16][LDS]
+  bf16* kbuf = qlo + 16 * LDS;                            // [2][64][LDS]
+  bf16* pbuf = kbuf + 2 * LATENT_CHUNK * LDS;             // [16][72]
+  float* wmax = reinterpret_cast<float*>(pbuf + 16 * LATENT_PLD);  // [4][16]
+  float* wsum = wmax + 64;                                // [4][16]
+  const int t = blockIdx.x, h0 = blockIdx.y * 16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q4 = lane & 3;
+  const int p = positions[t];
+  const int32_t* bt = block_table + (long long)row_seq[t] * bt_stride;
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int nchunks = (p - lo) / LATENT_CHUNK + 1;
+  const int cpr = RP / 8;  // 16-byte pieces of a cached row
+
+  auto load_chunk = [&](int c, int buf) {
+    const int j0 = lo + c * LATENT_CHUNK, n = min(LATENT_CHUNK, p + 1 - j0);
+    bf16* kb = kbuf + (long long)buf * LATENT_CHUNK * LDS;
+    for (int j = warp; j < LATENT_CHUNK; j += 4) {
+      bf16* dst = kb + j * LDS;
+      if (j < n) {
+        const int pos = j0 + j;
+        const bf16* src = cache + ((long long)bt[pos / block_size] * block_size + pos % block_size) * RP;
+        for (int ck = lane; ck < cpr; ck += 32) cp_async16(dst + ck * 8, src + ck * 8);
+      } else {
+        for (int ck = lane; ck < cpr; ck += 32) *reinterpret_cast<uint4*>(dst + ck * 8) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    cp_async_commit();
+  };
+
+  load_chunk(0, 0);
+  for (int e = tid; e < 16 * RP; e += 128) {
+    const int r = e / RP, d = e % RP, hh = h0 + r;
+    const float v = hh < heads ? qa[((long long)t * heads + hh) * RP + d] * scale : 0.f;
+    const bf16 hi = __float2bfloat16_rn(v);
+    qhi[r * LDS + d] = hi;
+    qlo[r * LDS + d] = __float2bfloat16_rn(v - __bfloat162float(hi));
+  }
+  const uint32_t qhi_s = smem_u32(qhi), qlo_s = smem_u32(qlo), p_s = smem_u32(pbuf);
+  const uint32_t a_off = (uint32_t)(((lane & 15) * LDS + (lane >> 4) * 8) * 2);
+  const uint32_t kq_off = (uint32_t)(((16 * warp + (lane & 7) + 8 * (lane >> 4)) * LDS + 8 * ((lane >> 3) & 1)) * 2);
+  const uint32_t pa_off = (uint32_t)(((lane & 15) * LATENT_PLD + (lane >> 4) * 8) * 2);
+  const int ntw = R / 32, dim_w = warp * (R / 4);
+  float m_[2] = {-INFINITY, -INFINITY}, l_[2] = {0.f, 0.f};
+  float o[NTW][4];
+#pragma unroll
+  for (int i = 0; i < NTW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int buf = c & 1;
+    cp_async_wait_all();
+    __syncthreads();  // chunk c (and, first time, the query) is in shared memory; chunk c-1 is done with
+    if (c + 1 < nchunks) load_chunk(c + 1, buf ^ 1);
+    const int n = min(LATENT_CHUNK, p + 1 - (lo + c * LATENT_CHUNK));
+    const uint32_t kb_s = smem_u32(kbuf + (long long)buf * LATENT_CHUNK * LDS);
+    // ---- scores of this warp's 16 keys: S = (Qhi + Qlo) K^T ----
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    for (int ks = 0; ks < RP / 16; ++ks) {
+      uint32_t a0, a1, a2, a3, c0, c1, c2, c3, b0, b1, b2, b3;
+      ldsm_x4(qhi_s + a_off + ks * 32, a0, a1, a2, a3);
+      ldsm_x4(qlo_s + a_off + ks * 32, c0, c1, c2, c3);
+      ldsm_x4(kb_s + kq_off + ks * 32, b0, b1, b2, b3);
+      mma_bf16_16816(s[0], a0, a1, a2, a3, b0, b1);
+      mma_bf16_16816(s[1], a0, a1, a2, a3, b2, b3);
+      mma_bf16_16816(s[0], c0, c1, c2, c3, b0, b1);
+      mma_bf16_16816(s[1], c0, c1, c2, c3, b2, b3);
+    }
+    // ---- online softmax over the chunk: rows g and g + 8 of this thread ----
+    float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = 16 * warp + nt * 8 + 2 * q4 + (e & 1);
+        if (key >= n) s[nt][e] = -INFINITY;
+        rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 1));
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 2));
+      if (q4 == 0) wmax[warp * 16 + g + 8 * r] = rmax[r];
+    }
+    __syncthreads();
+    float corr[2], psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
+      const float cm = fmaxf(fmaxf(wmax[row], wmax[16 + row]), fmaxf(wmax[32 + row], wmax[48 + row]));
+      const float mn = fmaxf(m_[r], cm);
+      corr[r] = expf(m_[r] - mn);
+      m_[r] = mn;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const float p0 = expf(s[nt][0] - m_[0]), p1 = expf(s[nt][1] - m_[0]);
+      const float p2 = expf(s[nt][2] - m_[1]), p3 = expf(s[nt][3] - m_[1]);
+      psum[0] += p0 + p1;
+      psum[1] += p2 + p3;
+      const int col = 16 * warp + nt * 8 + 2 * q4;
+      *reinterpret_cast<uint32_t*>(pbuf + g * LATENT_PLD + col) = pack_bf16x2(p0, p1);
+      *reinterpret_cast<uint32_t*>(pbuf + (g + 8) * LATENT_PLD + col) = pack_bf16x2(p2, p3);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+      if (q4 == 0) wsum[warp * 16 + g + 8 * r] = psum[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
+      l_[r] = l_[r] * corr[r] + ((wsum[row] + wsum[16 + row]) + (wsum[32 + row] + wsum[48 + row]));
+    }
+    // ---- output dims of this warp: O = O * corr + P V ----
+#pragma unroll
+    for (int i = 0; i < NTW; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < LATENT_CHUNK / 16; ++kk) {
+      uint32_t a0, a1, a2, a3;
+      ldsm_x4(p_s + pa_off + kk * 32, a0, a1, a2, a3);
+      const int key = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const uint32_t v_row = kb_s + (uint32_t)((key * LDS + dim_w + 8 * (lane >> 4)) * 2);
+#pragma unroll
+      for (int nd2 = 0; nd2 < NTW / 2; ++nd2) {
+        if (2 * nd2 < ntw) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(v_row + nd2 * 32, b0, b1, b2, b3);
+          mma_bf16_16816(o[2 * nd2], a0, a1, a2, a3, b0, b1);
+          mma_bf16_16816(o[2 * nd2 + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+  }
+  const float inv[2] = {1.f / l_[0], 1.f / l_[1]};
+#pragma unroll
+  for (int i = 0; i < NTW; ++i) {
+    if (i < ntw) {
+      const int dim = dim_w + i * 8 + 2 * q4;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int hh = h0 + g + 8 * r;
+        if (hh < heads)
+          *reinterpret_cast<uint32_t*>(out + ((long long)t * heads + hh) * R + dim) =
+              pack_bf16x2(o[i][2 * r] * inv[r], o[i][2 * r + 1] * inv[r]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // generalized delta rule.  One CTA per (sequence, head), thread j owns column j of the state S[key][value]
 // (kept in shared memory for the tokens of this step, loaded from / stored to the sequence's fp32 state
 // slot; a sequence whose first token this step is position 0 starts from zero, whatever the slot held).
@@ -420,6 +637,70 @@ __global__ void delta_rule_kernel(const T* __restrict__ proj, int ldp, const T* 
   }
   __syncthreads();
   for (int e = i; e < D * D; e += blockDim.x) st[e] = S[e];
+}
+
+// The same recurrence with the state column of every thread in REGISTERS (D known at compile time): the
+// per-token loops are pure FMA chains against broadcast reads of the token's vectors, no shared-memory
+// traffic for S.  Used for D = 32, 64, 128; other sizes take delta_rule_kernel.
+template <typename T, int D>
+__global__ void __launch_bounds__(D) delta_rule_reg_kernel(const T* __restrict__ proj, int ldp, const T* __restrict__ w2,
+                                                           const float* __restrict__ w0,
+                                                           const float* __restrict__ a_bias,
+                                                           const float* __restrict__ out_norm,
+                                                           float* __restrict__ state, long long slot_stride,
+                                                           const int32_t* __restrict__ seq_desc, int heads, int Rk,
+                                                           float eps, T* __restrict__ out) {
+  extern __shared__ float sm[];
+  float* kv_ = sm;                // k
+  float* us = kv_ + D;            // unit key
+  float* aus = us + D;            // a * u
+  float* wd = aus + D;            // decay
+  float* rs = wd + D;             // receptance
+  float* w2s = rs + D;            // [Rk][D+1]
+  float* zt = w2s + (long long)Rk * (D + 1);  // [Rk]
+  float* red = zt + Rk;           // [32]
+  const int seq = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
+  const int row0 = seq_desc[4 * seq + 0], n = seq_desc[4 * seq + 1], pos0 = seq_desc[4 * seq + 2],
+            slot = seq_desc[4 * seq + 3];
+  const int HD = heads * D, c = h * D + i;
+  float* st = state + (long long)slot * slot_stride + (long long)h * D * D;
+  float S[D];
+#pragma unroll
+  for (int q = 0; q < D; ++q) S[q] = pos0 > 0 ? st[q * D + i] : 0.f;
+  for (int e = i; e < Rk * D; e += D) {  // coalesced over the inner (rank) index of w2 [HD, Rk]
+    const int ch = e / Rk, r = e % Rk;
+    w2s[r * (D + 1) + ch] = ldf(w2 + (long long)(h * D + ch) * Rk + r);
+  }
+  const float w0c = w0[c], abc = a_bias[c], onc = out_norm[c];
+  for (int tt = 0; tt < n; ++tt) {
+    const T* pr = proj + (long long)(row0 + tt) * ldp;
+    for (int r = i; r < Rk; r += D) zt[r] = tanhf(ldf(pr + 5 * HD + r));
+    const float kk = ldf(pr + HD + c), rv = ldf(pr + c), vj = ldf(pr + 2 * HD + c);
+    const float av = sigmoidf_(ldf(pr + 4 * HD + c) + abc), gv = sigmoidf_(ldf(pr + 3 * HD + c));
+    const float ssk = block_sum(kk * kk, red);  // (its barriers also publish zt)
+    float z = w0c;
+    for (int r = 0; r < Rk; ++r) z = fmaf(w2s[r * (D + 1) + i], zt[r], z);
+    const float uu = kk / sqrtf(ssk + 1e-6f);
+    kv_[i] = kk;
+    us[i] = uu;
+    aus[i] = av * uu;
+    wd[i] = expf(-0.6065306597126334f * sigmoidf_(z));
+    rs[i] = rv;
+    __syncthreads();
+    float uS = 0.f;
+#pragma unroll
+    for (int q = 0; q < D; ++q) uS = fmaf(us[q], S[q], uS);
+    float o = 0.f;
+#pragma unroll
+    for (int q = 0; q < D; ++q) {
+      S[q] = wd[q] * S[q] - aus[q] * uS + kv_[q] * vj;
+      o = fmaf(S[q], rs[q], o);
+    }
+    const float sso = block_sum(o * o, red);  // (its barriers keep the next token's writes behind these reads)
+    stf(out + (long long)(row0 + tt) * HD + c, o / sqrtf(sso / (float)D + eps) * onc * gv);
+  }
+#pragma unroll
+  for (int q = 0; q < D; ++q) st[q * D + i] = S[q];
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -674,6 +955,15 @@ int b200q_centered_rmsnorm(const float* x, const int32_t* rows, const float* w1,
 // the general form behind b200q_linear / _batched / _grouped
 static int launch_linear(const LinearArgs& a, int tiles_m, int nz, int dtype, int out_f32, void* stream) {
   if (tiles_m <= 0 || nz <= 0 || a.N <= 0) return B200Q_OK;
+  if (nz == 1 && !a.group_off && a.N <= 64) {
+    const long long warps = (long long)a.M * ((a.N + 7) / 8);
+    const unsigned blocks = (unsigned)((warps + 7) / 8);
+    if (dtype == B200Q_DTYPE_F32) skinny_linear_kernel<float, float><<<blocks, 256, 0, as_stream(stream)>>>(a);
+    else if (out_f32) skinny_linear_kernel<bf16, float><<<blocks, 256, 0, as_stream(stream)>>>(a);
+    else skinny_linear_kernel<bf16, bf16><<<blocks, 256, 0, as_stream(stream)>>>(a);
+    B200Q_LAUNCH_CHECK();
+    return B200Q_OK;
+  }
   dim3 grid((a.N + 63) / 64, tiles_m, nz);
   B200Q_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "linear: grid too large (rows=%d groups=%d)", a.M, nz);
   if (dtype == B200Q_DTYPE_F32) {
@@ -771,6 +1061,33 @@ int b200q_latent_attn(const float* qa, const void* cache, const int32_t* block_t
   const int RP = kv_rank + rot_dim;
   const size_t smem = (size_t)(8 * RP + 32 * (RP + 1)) * sizeof(float);
   B200Q_CHECK_ARG(smem <= 227 * 1024, "latent_attn: kv_rank + rot_dim = %d does not fit shared memory", RP);
+  // bf16 caches whose sizes fit the tensor-core tiles (B200Q_LATENT_MMA=0: the scalar kernel everywhere)
+  static const bool use_mma = [] {
+    const char* v = getenv("B200Q_LATENT_MMA");
+    return !(v && v[0] == '0');
+  }();
+  if (use_mma && dtype == B200Q_DTYPE_BF16 && kv_rank % 64 == 0 && kv_rank <= 512 && RP % 16 == 0 &&
+      (reinterpret_cast<uintptr_t>(cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0) {
+    const int LDS = RP + 8;
+    const size_t sm2 = (size_t)(32 + 2 * LATENT_CHUNK) * LDS * 2 + 16 * LATENT_PLD * 2 + 128 * sizeof(float);
+    if (sm2 <= 227 * 1024) {
+      dim3 grid2(T_, (heads + 15) / 16);
+#define LATENT_MMA(NTW)                                                                                           \
+  do {                                                                                                            \
+    B200Q_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                    (int)sm2));                                                                   \
+    latent_attn_mma_kernel<NTW><<<grid2, 128, sm2, as_stream(stream)>>>(                                          \
+        qa, (const bf16*)cache, block_table, bt_stride, row_seq, positions, heads, kv_rank, rot_dim, block_size, \
+        window, scale, (bf16*)out);                                                                               \
+  } while (0)
+      if (kv_rank <= 128) LATENT_MMA(4);
+      else if (kv_rank <= 256) LATENT_MMA(8);
+      else LATENT_MMA(16);
+#undef LATENT_MMA
+      B200Q_LAUNCH_CHECK();
+      return B200Q_OK;
+    }
+  }
   dim3 grid(T_, (heads + 7) / 8);
 #define LATENT_LAUNCH(TT, ACC)                                                                                     \
   do {                                                                                                             \
@@ -802,11 +1119,35 @@ int b200q_delta_rule(const void* proj, int ldp, const void* w2, const float* w0,
                       Rk > 0 && n_seqs >= 0 && is_dtype(dtype),
                   "delta_rule: bad argument");
   if (n_seqs == 0) return B200Q_OK;
+  dim3 grid(n_seqs, heads);
+  if (D == 32 || D == 64 || D == 128) {
+    const size_t smem = (5 * (size_t)D + (size_t)Rk * (D + 1) + Rk + 32) * sizeof(float);
+    B200Q_CHECK_ARG(smem <= 227 * 1024, "delta_rule: decay rank %d does not fit shared memory", Rk);
+#define DELTA_REG(TT, DD)                                                                                        \
+  do {                                                                                                           \
+    B200Q_CUDA(cudaFuncSetAttribute(delta_rule_reg_kernel<TT, DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                    (int)smem));                                                                 \
+    delta_rule_reg_kernel<TT, DD><<<grid, DD, smem, as_stream(stream)>>>(                                        \
+        (const TT*)proj, ldp, (const TT*)w2, w0, a_bias, out_norm, state, slot_stride, seq_desc, heads, Rk, eps, \
+        (TT*)out);                                                                                               \
+  } while (0)
+#define DELTA_BY_D(TT)                    \
+  do {                                    \
+    if (D == 32) DELTA_REG(TT, 32);       \
+    else if (D == 64) DELTA_REG(TT, 64);  \
+    else DELTA_REG(TT, 128);              \
+  } while (0)
+    if (dtype == B200Q_DTYPE_F32) DELTA_BY_D(float);
+    else DELTA_BY_D(bf16);
+#undef DELTA_BY_D
+#undef DELTA_REG
+    B200Q_LAUNCH_CHECK();
+    return B200Q_OK;
+  }
   const int threads = (D + 31) & ~31;
   B200Q_CHECK_ARG(threads <= 1024, "delta_rule: dim=%d unsupported (<= 1024)", D);
   const size_t smem = ((size_t)D * D + 5 * (size_t)D + (size_t)Rk * D + Rk + 32) * sizeof(float);
   B200Q_CHECK_ARG(smem <= 227 * 1024, "delta_rule: a %dx%d state (+ rank %d) does not fit shared memory", D, D, Rk);
-  dim3 grid(n_seqs, heads);
   if (dtype == B200Q_DTYPE_F32) {
     B200Q_CUDA(cudaFuncSetAttribute(delta_rule_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     delta_rule_kernel<float><<<grid, threads, smem, as_stream(stream)>>>(

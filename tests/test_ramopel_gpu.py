@@ -187,22 +187,47 @@ def test_tensor_core_shapes_through_the_model(cuda):
 
 
 # ---- latent attention kernel with made-up inputs: one key stands out ------------------------------------
-def _latent_attn(cuda, qa, rows, pos, table, window, scale, R, P, bs=16):
+def _latent_attn(cuda, qa, rows, pos, table, window, scale, R, P, bs=16, dtype=torch.float32):
     """qa [n, H, R+P] at positions pos of ONE sequence whose cached rows [L, R+P] lie in shuffled pages"""
     L, lib = _ops()
     n, H = qa.shape[0], qa.shape[1]
     n_blocks = int(max(table)) + 1
-    cache = torch.full((n_blocks * bs, R + P), 1e4)               # whatever is not written is poison
+    cache = torch.full((n_blocks * bs, R + P), 1e4, dtype=dtype)  # whatever is not written is poison
     for j in range(rows.shape[0]):
         cache[table[j // bs] * bs + j % bs] = rows[j]
     bt = torch.tensor([table], dtype=torch.int32, device=cuda)
-    out = torch.zeros(n, H, R, device=cuda)
+    out = torch.zeros(n, H, R, device=cuda, dtype=dtype)
     qd, cd = qa.to(cuda).contiguous(), cache.to(cuda)
     rs, ps = torch.zeros(n, dtype=torch.int32, device=cuda), torch.tensor(pos, dtype=torch.int32, device=cuda)
     L.check(lib.b200q_latent_attn(qd.data_ptr(), cd.data_ptr(), bt.data_ptr(), bt.shape[1], rs.data_ptr(),
-                                  ps.data_ptr(), n, H, R, P, bs, window, scale, out.data_ptr(), L.DTYPE_F32, None))
+                                  ps.data_ptr(), n, H, R, P, bs, window, scale, out.data_ptr(),
+                                  L.DTYPE_F32 if dtype == torch.float32 else L.DTYPE_BF16, None))
     torch.cuda.synchronize()
-    return out.cpu()
+    return out.float().cpu()
+
+
+@pytest.mark.parametrize("window,H,R,P", [(0, 9, 64, 16), (70, 18, 128, 32), (64, 16, 192, 16), (5, 3, 64, 0)])
+def test_latent_attn_tensor_core_kernel(cuda, window, H, R, P):
+    """the bf16 tensor-core kernel: random queries over hundreds of keys, and queries that single out one key
+    (first key, chunk and page borders, window edge) — against the plain fp64 form on the same bf16 rows"""
+    Lq, bs = 300, 16
+    g = torch.Generator().manual_seed(6)
+    rows = torch.randn(Lq, R + P, generator=g).to(torch.bfloat16)
+    table = torch.randperm(Lq // bs + 1, generator=g).tolist()
+    pos = [0, 1, 15, 16, 63, 64, 65, 127, 128, 129, 200, 299]
+    qa = torch.randn(len(pos), H, R + P, generator=g) * 0.5
+    got = _latent_attn(cuda, qa, rows, pos, table, window, 0.3, R, P, bs, torch.bfloat16)
+    want = O.windowed_attention(qa.double(), rows.double(), rows[:, :R].double(), torch.tensor(pos), window, 0.3)
+    assert rel_err(got.reshape(len(pos), -1), want.reshape(len(pos), -1)) < 2e-2
+    unit = rows.float() / rows.float().norm(dim=-1, keepdim=True) ** 2
+    for back in sorted({0, 1, 63, 64, 65, 128, max(window - 1, 0), window, window + 1}):
+        ps = [p for p in pos if p - back >= 0]
+        if not ps:
+            continue
+        q1 = torch.stack([unit[p - back] for p in ps])[:, None, :].repeat(1, H, 1) * 80.0
+        got = _latent_attn(cuda, q1, rows, ps, table, window, 1.0, R, P, bs, torch.bfloat16)
+        want = O.windowed_attention(q1.double(), rows.double(), rows[:, :R].double(), torch.tensor(ps), window, 1.0)
+        assert rel_err(got.reshape(len(ps), -1), want.reshape(len(ps), -1)) < 2e-2, (window, back)
 
 
 @pytest.mark.parametrize("window", [0, 1, 16, 17, 50])
@@ -230,11 +255,12 @@ def test_latent_attn_standout_key(cuda, window):
         assert (hit < 1e-3) == seen, (window, back, float(hit))
 
 
-def test_delta_rule_op_state_slots(cuda):
+@pytest.mark.parametrize("D", [24, 32, 64, 128])
+def test_delta_rule_op_state_slots(cuda, D):
     """the recurrence kernel alone: two sequences in one launch, one continuing from its slot and one starting
     (position 0) in a slot that holds another sequence's leftovers"""
     L, lib = _ops()
-    H, D, Rk, eps = 3, 24, 4, 1e-5
+    H, Rk, eps = 3, 4 if D < 64 else 37, 1e-5
     HD, NP = H * D, 5 * H * D + Rk
     g = torch.Generator().manual_seed(4)
     n_a, n_b, n_a2 = 13, 7, 5
