@@ -252,11 +252,13 @@ int b200q_latent_attn(const float* qa_dev, const void* cache_dev, const int32_t*
  *     [r | k | v | g | a | z] (heads*D each, z: Rk); state: fp32 [slots] x slot_stride, this layer's part
  *     [heads][D][D] at the start of a slot.  Per token and head:
  *     w = exp(-e^-1/2 sigmoid(w0 + W2 tanh z)), a = sigmoid(a + a_bias), u = k / sqrt(sum k^2 + 1e-6),
- *     S <- diag(w) S - (a*u)(u^T S) + k v^T, o = S^T r, out = o / rms(o) * out_norm * sigmoid(g) */
+ *     S <- diag(w) S - (a*u)(u^T S) + k v^T, o = S^T r, out = o / rms(o) * out_norm * sigmoid(g).
+ *     scratch (fp32, 6*T*heads*D, may be NULL) with the step's row count T lets D = 32/64/128 run as three
+ *     launches: the state-independent vectors of all T rows at once, the bare recurrence, norm and gate */
 int b200q_delta_rule(const void* proj_dev, int ldp, const void* w2_dev, const float* w0_dev,
                      const float* a_bias_dev, const float* out_norm_dev, float* state_dev, long long slot_stride,
                      const int32_t* seq_desc_dev, int n_seqs, int heads, int D, int Rk, float eps, void* out_dev,
-                     int dtype, void* stream);
+                     int dtype, float* scratch_dev, int T, void* stream);
 /* PolyNorm over rows of F values: y = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3, N(v) = v / sqrt(mean(v^2) + eps) */
 int b200q_polynorm(const void* z_dev, const float* coef_dev, void* y_dev, int rows, int F, float eps, int dtype,
                    void* stream);

@@ -67,7 +67,7 @@ int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
 // widest use of every workspace buffer over the layers
 struct Widths {
   int64_t proj = 1, cq = 1, q = 1, qa = 1, olat = 1, attn = 1, ffh = 1, ffa = 1, experts = 1, pairs = 1, egu = 1,
-          eact = 1;
+          eact = 1, delta = 0;
   bool moe = false, shared = false;
 };
 Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_layer>& Ls) {
@@ -85,6 +85,7 @@ Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_la
     } else {
       w.proj = std::max<int64_t>(w.proj, 5 * (int64_t)d.heads * d.dim + d.decay_rank);
       w.attn = std::max<int64_t>(w.attn, (int64_t)d.heads * d.dim);
+      w.delta = std::max<int64_t>(w.delta, (int64_t)d.heads * d.dim);
     }
     if (d.ff == B200Q_FF_POLYNORM) {
       w.ffh = std::max<int64_t>(w.ffh, d.ff_dim);
@@ -128,6 +129,7 @@ int64_t layout(b200q_model* m, uint8_t* base) {
   y->qa = (float*)take(T * w.qa * 4);
   y->olat = take(T * w.olat * es);
   y->attn = take(T * w.attn * es);
+  y->dscr = (float*)take(w.delta ? T * w.delta * 6 * 4 : 1);
   y->ffh = take(T * w.ffh * es);
   y->ffa = take(T * w.ffa * es);
   y->rlog = (float*)take(T * w.experts * 4);
@@ -391,7 +393,8 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
       TRY(B200Q_PROF_PREFILL_ATTN, 0.0,
           b200q_delta_rule(y->proj, NP, l.w2, l.w0, l.a_bias, l.out_norm, y->state + l.state_off,
                            y->state_slot_floats, b->seq_desc, b->n_rows, d.heads, d.dim, d.decay_rank, c.rms_eps,
-                           y->attn, dt, stream));
+                           y->attn, dt, T > b->n_rows ? y->dscr : nullptr /* portions of prompts: three launches */, T,
+                           stream));
       LIN(y->attn, HD, l.o, nullptr, y->mix, W, W, HD, 0);
     }
     // ---- feed-forward and the layer's sum ----

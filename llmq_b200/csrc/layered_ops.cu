@@ -187,12 +187,35 @@ __global__ void __launch_bounds__(256) skinny_linear_kernel(LinearArgs a) {
   float acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-  for (int k = lane; k < a.K; k += 32) {
-    const float av = ldf(A + k);
+  bool vec_done = false;
+  if constexpr (sizeof(T) == 2) {
+    // bf16 rows whose start is 16-byte aligned: 8 elements per load
+    if (a.K % 8 == 0 && a.lda % 8 == 0 && ((reinterpret_cast<uintptr_t>(a.A) | reinterpret_cast<uintptr_t>(a.W)) & 15) == 0) {
+      for (int k = lane * 8; k < a.K; k += 256) {
+        const uint4 av = ld_v4(A + k);
+        const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      if (n0 + j < a.N) acc[j] = fmaf(av, ldf(Wm + (long long)(n0 + j) * a.K + k), acc[j]);
+        for (int j = 0; j < 8; ++j)
+          if (n0 + j < a.N) {
+            const uint4 wv = ld_nc_v4(Wm + (long long)(n0 + j) * a.K + k);
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              acc[j] = fmaf(bf16_lo(aw[e]), bf16_lo(ww[e]), acc[j]);
+              acc[j] = fmaf(bf16_hi(aw[e]), bf16_hi(ww[e]), acc[j]);
+            }
+          }
+      }
+      vec_done = true;
+    }
   }
+  if (!vec_done)
+    for (int k = lane; k < a.K; k += 32) {
+      const float av = ldf(A + k);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (n0 + j < a.N) acc[j] = fmaf(av, ldf(Wm + (long long)(n0 + j) * a.K + k), acc[j]);
+    }
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float v = warp_sum(acc[j]);
@@ -418,11 +441,19 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const float* __res
   auto load_chunk = [&](int c, int buf) {
     const int j0 = lo + c * LATENT_CHUNK, n = min(LATENT_CHUNK, p + 1 - j0);
     bf16* kb = kbuf + (long long)buf * LATENT_CHUNK * LDS;
+    // lane l looks up the pages of rows l and l + 32 of the chunk once (one division each); the warp then
+    // walks its rows (warp, warp + 4, ...) with the row's cache index broadcast from the lane that holds it
+    long long src_row[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int j = lane + 32 * k, pos = j0 + j;
+      src_row[k] = j < n ? (long long)bt[pos / block_size] * block_size + pos % block_size : -1;
+    }
     for (int j = warp; j < LATENT_CHUNK; j += 4) {
+      const long long row = __shfl_sync(0xffffffffu, j < 32 ? src_row[0] : src_row[1], j & 31);
       bf16* dst = kb + j * LDS;
-      if (j < n) {
-        const int pos = j0 + j;
-        const bf16* src = cache + ((long long)bt[pos / block_size] * block_size + pos % block_size) * RP;
+      if (row >= 0) {
+        const bf16* src = cache + row * RP;
         for (int ck = lane; ck < cpr; ck += 32) cp_async16(dst + ck * 8, src + ck * 8);
       } else {
         for (int ck = lane; ck < cpr; ck += 32) *reinterpret_cast<uint4*>(dst + ck * 8) = make_uint4(0, 0, 0, 0);
@@ -701,6 +732,121 @@ __global__ void __launch_bounds__(D) delta_rule_reg_kernel(const T* __restrict__
   }
 #pragma unroll
   for (int q = 0; q < D; ++q) st[q * D + i] = S[q];
+}
+
+// ------------------------------------------------------------------------------------------------
+// The delta rule in three launches (D = 32, 64, 128).  Everything that does not depend on the state is
+// computed for all tokens at once, so the sequential kernel is a bare chain of FMAs on a register-resident
+// state column with no barrier per token:
+//   prepare   (CTA per token x head): vec[t,h] = {k, u, a*u, w, r}  (fp32, 5 x D)
+//   recur     (CTA per sequence x head, thread j = value column j): S <- diag(w) S - (a*u)(u^T S) + k v_j,
+//             o_j = sum_q S[q] r[q]  -> raw[t, h*D + j] (fp32)
+//   finish    (CTA per token x head): out = raw / rms(raw) * out_norm * sigmoid(g)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void delta_prepare_kernel(const T* __restrict__ proj, int ldp, const T* __restrict__ w2,
+                                     const float* __restrict__ w0, const float* __restrict__ a_bias, int heads, int D,
+                                     int Rk, float* __restrict__ vec) {
+  extern __shared__ float sm[];
+  float* zt = sm;        // [Rk]
+  float* red = zt + Rk;  // [32]
+  const int t = blockIdx.x, h = blockIdx.y, i = threadIdx.x, HD = heads * D, c = h * D + i;
+  const T* pr = proj + (long long)t * ldp;
+  for (int r = i; r < Rk; r += blockDim.x) zt[r] = tanhf(ldf(pr + 5 * HD + r));
+  const float kk = ldf(pr + HD + c);
+  const float ssk = block_sum(kk * kk, red);  // (its barriers also publish zt)
+  float z = w0[c];
+  const T* wr = w2 + (long long)c * Rk;
+  for (int r = 0; r < Rk; ++r) z = fmaf(ldf(wr + r), zt[r], z);
+  const float uu = kk / sqrtf(ssk + 1e-6f);
+  float* o = vec + ((long long)t * heads + h) * 5 * D;
+  o[i] = kk;
+  o[D + i] = uu;
+  o[2 * D + i] = sigmoidf_(ldf(pr + 4 * HD + c) + a_bias[c]) * uu;
+  o[3 * D + i] = expf(-0.6065306597126334f * sigmoidf_(z));
+  o[4 * D + i] = ldf(pr + c);
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(D) delta_recur_kernel(const T* __restrict__ proj, int ldp,
+                                                        const float* __restrict__ vec, float* __restrict__ state,
+                                                        long long slot_stride, const int32_t* __restrict__ seq_desc,
+                                                        int heads, float* __restrict__ raw) {
+  // the per-token vectors of DELTA_G tokens at a time come into shared memory by cp.async, one group ahead
+  // of the one being consumed, so the chain below never waits for global memory
+  constexpr int G = 8, TOK = 5 * D;                 // floats per token
+  __shared__ __align__(16) float sv[2][G][TOK];
+  const int seq = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
+  const int row0 = seq_desc[4 * seq + 0], n = seq_desc[4 * seq + 1], pos0 = seq_desc[4 * seq + 2],
+            slot = seq_desc[4 * seq + 3];
+  const int HD = heads * D, c = h * D + i;
+  float* st = state + (long long)slot * slot_stride + (long long)h * D * D;
+  auto fetch = [&](int g0, int buf) {
+    const int cnt = min(G, n - g0);
+    for (int e = i; e < cnt * (TOK / 4); e += D) {
+      const int tt = e / (TOK / 4), pc = e % (TOK / 4);
+      cp_async16(&sv[buf][tt][pc * 4], vec + ((long long)(row0 + g0 + tt) * heads + h) * TOK + pc * 4);
+    }
+    cp_async_commit();
+  };
+  fetch(0, 0);
+  float S[D];
+#pragma unroll
+  for (int q = 0; q < D; ++q) S[q] = pos0 > 0 ? st[q * D + i] : 0.f;
+  for (int g0 = 0, buf = 0; g0 < n; g0 += G, buf ^= 1) {
+    const int cnt = min(G, n - g0);
+    float vj[G];
+#pragma unroll
+    for (int tt = 0; tt < G; ++tt)
+      vj[tt] = tt < cnt ? ldf(proj + (long long)(row0 + g0 + tt) * ldp + 2 * HD + c) : 0.f;
+    cp_async_wait_all();
+    __syncthreads();  // this group has landed; the other buffer is no longer read
+    if (g0 + G < n) fetch(g0 + G, buf ^ 1);
+#pragma unroll
+    for (int tt = 0; tt < G; ++tt) {
+      if (tt < cnt) {
+        const float4* v4 = reinterpret_cast<const float4*>(&sv[buf][tt][0]);
+        float u0 = 0.f, u1 = 0.f, u2 = 0.f, u3 = 0.f;
+#pragma unroll
+        for (int q = 0; q < D / 4; ++q) {
+          const float4 u = v4[D / 4 + q];
+          u0 = fmaf(u.x, S[4 * q], u0);
+          u1 = fmaf(u.y, S[4 * q + 1], u1);
+          u2 = fmaf(u.z, S[4 * q + 2], u2);
+          u3 = fmaf(u.w, S[4 * q + 3], u3);
+        }
+        const float uS = (u0 + u1) + (u2 + u3), vv = vj[tt];
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+        for (int q = 0; q < D / 4; ++q) {
+          const float4 k = v4[q], au = v4[2 * (D / 4) + q], w = v4[3 * (D / 4) + q], r = v4[4 * (D / 4) + q];
+          S[4 * q] = w.x * S[4 * q] - au.x * uS + k.x * vv;
+          S[4 * q + 1] = w.y * S[4 * q + 1] - au.y * uS + k.y * vv;
+          S[4 * q + 2] = w.z * S[4 * q + 2] - au.z * uS + k.z * vv;
+          S[4 * q + 3] = w.w * S[4 * q + 3] - au.w * uS + k.w * vv;
+          o0 = fmaf(S[4 * q], r.x, o0);
+          o1 = fmaf(S[4 * q + 1], r.y, o1);
+          o2 = fmaf(S[4 * q + 2], r.z, o2);
+          o3 = fmaf(S[4 * q + 3], r.w, o3);
+        }
+        raw[(long long)(row0 + g0 + tt) * HD + c] = (o0 + o1) + (o2 + o3);
+      }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < D; ++q) st[q * D + i] = S[q];
+}
+
+template <typename T>
+__global__ void delta_finish_kernel(const float* __restrict__ raw, const T* __restrict__ proj, int ldp,
+                                    const float* __restrict__ out_norm, int heads, int D, float eps,
+                                    T* __restrict__ out) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, h = blockIdx.y, i = threadIdx.x, HD = heads * D, c = h * D + i;
+  const float o = raw[(long long)t * HD + c];
+  const float sso = block_sum(o * o, red);
+  const float gv = sigmoidf_(ldf(proj + (long long)t * ldp + 3 * HD + c));
+  stf(out + (long long)t * HD + c, o / sqrtf(sso / (float)D + eps) * out_norm[c] * gv);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1114,11 +1260,37 @@ int b200q_latent_attn(const float* qa, const void* cache, const int32_t* block_t
 
 int b200q_delta_rule(const void* proj, int ldp, const void* w2, const float* w0, const float* a_bias,
                      const float* out_norm, float* state, long long slot_stride, const int32_t* seq_desc,
-                     int n_seqs, int heads, int D, int Rk, float eps, void* out, int dtype, void* stream) {
+                     int n_seqs, int heads, int D, int Rk, float eps, void* out, int dtype, float* scratch, int T_,
+                     void* stream) {
   B200Q_CHECK_ARG(proj && w2 && w0 && a_bias && out_norm && state && seq_desc && out && heads > 0 && D > 0 &&
                       Rk > 0 && n_seqs >= 0 && is_dtype(dtype),
                   "delta_rule: bad argument");
   if (n_seqs == 0) return B200Q_OK;
+  if (scratch && T_ > 0 && (D == 32 || D == 64 || D == 128)) {
+    // three launches: per-token vectors for all rows, the bare recurrence, norm and gate for all rows
+    float* vec = scratch;
+    float* raw = scratch + (long long)T_ * heads * D * 5;
+    dim3 tg(T_, heads), sg(n_seqs, heads);
+    cudaStream_t st = as_stream(stream);
+    const size_t psm = (size_t)(Rk + 32) * sizeof(float);
+    B200Q_CHECK_ARG(psm <= 48 * 1024, "delta_rule: decay rank %d too large", Rk);
+#define DELTA_SPLIT(TT)                                                                                           \
+  do {                                                                                                            \
+    delta_prepare_kernel<TT><<<tg, D, psm, st>>>((const TT*)proj, ldp, (const TT*)w2, w0, a_bias, heads, D, Rk, vec); \
+    if (D == 32)                                                                                                  \
+      delta_recur_kernel<TT, 32><<<sg, 32, 0, st>>>((const TT*)proj, ldp, vec, state, slot_stride, seq_desc, heads, raw); \
+    else if (D == 64)                                                                                             \
+      delta_recur_kernel<TT, 64><<<sg, 64, 0, st>>>((const TT*)proj, ldp, vec, state, slot_stride, seq_desc, heads, raw); \
+    else                                                                                                          \
+      delta_recur_kernel<TT, 128><<<sg, 128, 0, st>>>((const TT*)proj, ldp, vec, state, slot_stride, seq_desc, heads, raw); \
+    delta_finish_kernel<TT><<<tg, D, 0, st>>>(raw, (const TT*)proj, ldp, out_norm, heads, D, eps, (TT*)out);      \
+  } while (0)
+    if (dtype == B200Q_DTYPE_F32) DELTA_SPLIT(float);
+    else DELTA_SPLIT(bf16);
+#undef DELTA_SPLIT
+    B200Q_LAUNCH_CHECK();
+    return B200Q_OK;
+  }
   dim3 grid(n_seqs, heads);
   if (D == 32 || D == 64 || D == 128) {
     const size_t smem = (5 * (size_t)D + (size_t)Rk * (D + 1) + Rk + 32) * sizeof(float);

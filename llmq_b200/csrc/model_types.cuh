@@ -39,6 +39,7 @@ struct b200q_layered {
   int64_t n_slots = 0;
   float* tap = nullptr;
   // workspace views (element type = cfg.dtype unless float)
+  float *dscr = nullptr;  // delta rule: per-token vectors and raw outputs of a step (fp32)
   float *x = nullptr, *qa = nullptr, *rlog = nullptr, *wts = nullptr, *sgate = nullptr, *logits = nullptr;
   void *h1 = nullptr, *h2 = nullptr, *mix = nullptr, *ffo = nullptr, *proj = nullptr, *cq = nullptr, *q = nullptr,
        *olat = nullptr, *attn = nullptr, *ffh = nullptr, *ffa = nullptr, *egu = nullptr, *eact = nullptr,

@@ -180,7 +180,7 @@ SIGNATURES = {
     "b200q_latent_prep": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200q_rope_pairs_q": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b200q_latent_attn": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, _vp]),
-    "b200q_delta_rule": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp]),
+    "b200q_delta_rule": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _f, _vp, _i, _vp, _i, _vp]),
     "b200q_polynorm": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200q_clamped_glu": (_i, [_vp, _vp, _i64, _i, _f, _i, _vp]),
     "b200q_moe_route": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -255,8 +255,9 @@ def test_latent_attn_standout_key(cuda, window):
         assert (hit < 1e-3) == seen, (window, back, float(hit))
 
 
+@pytest.mark.parametrize("split", [False, True])
 @pytest.mark.parametrize("D", [24, 32, 64, 128])
-def test_delta_rule_op_state_slots(cuda, D):
+def test_delta_rule_op_state_slots(cuda, D, split):
     """the recurrence kernel alone: two sequences in one launch, one continuing from its slot and one starting
     (position 0) in a slot that holds another sequence's leftovers"""
     L, lib = _ops()
@@ -284,6 +285,7 @@ def test_delta_rule_op_state_slots(cuda, D):
     slot_floats = H * D * D + 10                                  # a slot may be wider than this layer's part
     state = torch.full((3, slot_floats), 7.0, device=cuda)        # leftovers everywhere
     out = torch.zeros(proj.shape[0], HD, device=cuda)
+    scratch = torch.zeros(6 * proj.shape[0] * HD, device=cuda)    # the three-launch form's per-token vectors
     dev = lambda t: t.to(cuda).contiguous()
     pj, w2d, w0d, abd, ond = dev(proj), dev(w2), dev(w0), dev(ab), dev(on)
 
@@ -291,7 +293,8 @@ def test_delta_rule_op_state_slots(cuda, D):
         sd_ = torch.tensor(desc, dtype=torch.int32, device=cuda)
         L.check(lib.b200q_delta_rule(pj.data_ptr(), NP, w2d.data_ptr(), w0d.data_ptr(), abd.data_ptr(), ond.data_ptr(),
                                      state.data_ptr(), slot_floats, sd_.data_ptr(), len(desc), H, D, Rk, eps,
-                                     out.data_ptr(), L.DTYPE_F32, None))
+                                     out.data_ptr(), L.DTYPE_F32, scratch.data_ptr() if split else None,
+                                     proj.shape[0], None))
         torch.cuda.synchronize()
 
     run([[0, n_a, 0, 2], [n_a, n_b, 0, 0]])                       # a in slot 2, b in slot 0, both from position 0
