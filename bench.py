@@ -596,7 +596,7 @@ def llama_of_equal_size(rspec):
     H, Lr = rspec.width, rspec.n_layers
     n_q, n_kv, D = max(H // 128, 1), max(min(8, H // 128), 1), 128
     attn = H * (n_q + 2 * n_kv) * D + H * n_q * D
-    per_layer = (rspec.weight_bytes_per_token() // 2 - 2 * rspec.vocab * H) / Lr
+    per_layer = (rspec.weight_bytes_per_token() // 2 - rspec.vocab * H) / Lr
     inter = max(256, int(round((per_layer - attn) / (3 * H) / 256)) * 256)
     return ModelSpec(hidden=H, n_layers=Lr, n_q_heads=n_q, n_kv_heads=n_kv, head_dim=D, intermediate=inter,
                      vocab=rspec.vocab, rope_theta=10000.0, tie_embeddings=False, max_position_embeddings=8192,
@@ -708,8 +708,10 @@ def run_compare(args):
         rk, lk = r["decode"]["kernel_ms_per_step"], l["decode"]["kernel_ms_per_step"]
         frac = lambda by, ms: round(by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3) if ms > 0 else None
         roof = {
-            "decode_weights": {"ramopel": frac(wb, rk["gemm"]), "llama": frac(lspec.weight_bytes_per_step(), lk["gemm"]),
-                               "unit": "fraction of measured HBM copy bandwidth, matrix bytes / gemm time"},
+            "decode_weights": {"ramopel": frac(rspec.weight_bytes_per_token(batch=B), rk["gemm"]),
+                               "llama": frac(lspec.weight_bytes_per_step() - 2 * lspec.vocab * lspec.hidden, lk["gemm"]),
+                               "unit": "fraction of measured HBM copy bandwidth, matrix bytes a step of this batch "
+                                       "touches (all experts the batch can reach) / gemm time"},
             "decode_attention": {"ramopel_latent": frac(cache_r, rk["decode_attn"]),
                                  "llama": frac(cache_l, lk["decode_attn"]),
                                  "unit": "fraction of measured HBM copy bandwidth, cache bytes / attention time"},

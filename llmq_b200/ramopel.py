@@ -156,9 +156,10 @@ class RamopelSpec:
         return {"architecture": ARCHITECTURE, "width": self.width, "vocab": self.vocab,
                 "norm": {"eps": self.rms_eps}, "embedding": {"scale": self.embed_scale}, "layers": out}
 
-    def weight_bytes_per_token(self, esize: int = 2) -> int:
-        """matrix bytes one decoded token touches (a routed layer reads `top_k` of its experts)"""
-        W, n = self.width, 2 * self.vocab * self.width
+    def weight_bytes_per_token(self, esize: int = 2, batch: int = 1) -> int:
+        """matrix bytes one decode step of `batch` tokens touches (a routed layer reads at most
+        min(experts, batch * top_k) of its experts; the embedding table is read by row, the head in full)"""
+        W, n = self.width, self.vocab * self.width
         for ly in self.layers:
             if ly.mixer == "latent_attention":
                 own = ly.kv_rank + ly.rot_dim if ly.kv_from < 0 else 0
@@ -170,7 +171,8 @@ class RamopelSpec:
             if ly.ff == "dense":
                 n += 2 * W * ly.ff_dim
             elif ly.ff == "moe":
-                n += W * ly.n_experts + 3 * W * ly.ff_dim * ly.top_k + 3 * W * ly.shared_dim + (W if ly.shared_dim else 0)
+                n += (W * ly.n_experts + 3 * W * ly.ff_dim * min(ly.n_experts, batch * ly.top_k) + 3 * W * ly.shared_dim
+                      + (W if ly.shared_dim else 0))
         return n * esize
 
 
