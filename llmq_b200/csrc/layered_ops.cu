@@ -589,6 +589,204 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const float* __res
 }
 
 // ------------------------------------------------------------------------------------------------
+// The same product with the query fragments held in REGISTERS (sizes with (kv_rank + rot_dim) % 64 == 0):
+// warp w owns a quarter of the key dimensions, keeps the hi / lo fragments of the 16 heads' queries for
+// that quarter for the whole kernel (KS k-steps), and scores all 64 keys of a chunk over its quarter; the
+// four partial score tiles are summed through shared memory in a fixed order, after which every warp holds
+// the full 16 x 64 score tile in accumulator layout — softmax and the bf16 weights need no further
+// exchange and feed the value product of the warp's output slice directly.  Against the kernel above:
+// a third of the ldmatrix traffic (the query is never re-read), two barriers per chunk instead of three.
+// ------------------------------------------------------------------------------------------------
+template <int NTW, int KS>
+__global__ void __launch_bounds__(128) latent_attn_mma2_kernel(const float* __restrict__ qa,
+                                                               const bf16* __restrict__ cache,
+                                                               const int32_t* __restrict__ block_table, int bt_stride,
+                                                               const int32_t* __restrict__ row_seq,
+                                                               const int32_t* __restrict__ positions, int heads, int R,
+                                                               int P, int block_size, int window, float scale,
+                                                               bf16* __restrict__ out) {
+  extern __shared__ __align__(16) uint8_t smraw[];
+  const int RP = R + P, LDS = RP + 8;
+  bf16* kbuf = reinterpret_cast<bf16*>(smraw);                                  // [2][64][LDS]
+  float* spart = reinterpret_cast<float*>(kbuf + 2 * LATENT_CHUNK * LDS);      // [4 warps][8 n-tiles][32 lanes][4]
+  bf16* qhi = kbuf + LATENT_CHUNK * LDS;                                        // staging in buffer 1: [16][LDS] x 2
+  bf16* qlo = qhi + 16 * LDS;
+  const int t = blockIdx.x, h0 = blockIdx.y * 16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q4 = lane & 3;
+  const int p = positions[t];
+  const int32_t* bt = block_table + (long long)row_seq[t] * bt_stride;
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int nchunks = (p - lo) / LATENT_CHUNK + 1;
+  const int cpr = RP / 8;
+
+  auto load_chunk = [&](int c, int buf) {
+    const int j0 = lo + c * LATENT_CHUNK, n = min(LATENT_CHUNK, p + 1 - j0);
+    bf16* kb = kbuf + (long long)buf * LATENT_CHUNK * LDS;
+    long long src_row[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int j = lane + 32 * k, pos = j0 + j;
+      src_row[k] = j < n ? (long long)bt[pos / block_size] * block_size + pos % block_size : -1;
+    }
+    for (int j = warp; j < LATENT_CHUNK; j += 4) {
+      const long long row = __shfl_sync(0xffffffffu, j < 32 ? src_row[0] : src_row[1], j & 31);
+      bf16* dst = kb + j * LDS;
+      if (row >= 0) {
+        const bf16* src = cache + row * RP;
+        for (int ck = lane; ck < cpr; ck += 32) cp_async16(dst + ck * 8, src + ck * 8);
+      } else {
+        for (int ck = lane; ck < cpr; ck += 32) *reinterpret_cast<uint4*>(dst + ck * 8) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    cp_async_commit();
+  };
+
+  load_chunk(0, 0);
+  for (int e = tid; e < 16 * RP; e += 128) {
+    const int r = e / RP, d = e % RP, hh = h0 + r;
+    const float v = hh < heads ? qa[((long long)t * heads + hh) * RP + d] * scale : 0.f;
+    const bf16 hi = __float2bfloat16_rn(v);
+    qhi[r * LDS + d] = hi;
+    qlo[r * LDS + d] = __float2bfloat16_rn(v - __bfloat162float(hi));
+  }
+  __syncthreads();
+  uint32_t qh[KS][4], ql[KS][4];
+  {
+    const uint32_t a_off = (uint32_t)(((lane & 15) * LDS + (lane >> 4) * 8 + warp * KS * 16) * 2);
+    const uint32_t qhi_s = smem_u32(qhi), qlo_s = smem_u32(qlo);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      ldsm_x4(qhi_s + a_off + ks * 32, qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3]);
+      ldsm_x4(qlo_s + a_off + ks * 32, ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3]);
+    }
+  }
+  const uint32_t kq_off = (uint32_t)((((lane & 7) + 8 * (lane >> 4)) * LDS + warp * KS * 16 + 8 * ((lane >> 3) & 1)) * 2);
+  const int ntw = R / 32, dim_w = warp * (R / 4);
+  float m_[2] = {-INFINITY, -INFINITY}, l_[2] = {0.f, 0.f};
+  float o[NTW][4];
+#pragma unroll
+  for (int i = 0; i < NTW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int buf = c & 1;
+    cp_async_wait_all();
+    __syncthreads();  // chunk c has landed; buffer buf^1 (first time: the query staging) and spart are free
+    if (c + 1 < nchunks) load_chunk(c + 1, buf ^ 1);
+    const int n = min(LATENT_CHUNK, p + 1 - (lo + c * LATENT_CHUNK));
+    const uint32_t kb_s = smem_u32(kbuf + (long long)buf * LATENT_CHUNK * LDS);
+    // ---- partial scores of all 64 keys over this warp's quarter of the dimensions ----
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {  // k-step outside: eight independent accumulator chains per pass
+      uint32_t b[4][4];
+#pragma unroll
+      for (int nt2 = 0; nt2 < 4; ++nt2)
+        ldsm_x4(kb_s + kq_off + (uint32_t)(nt2 * 16 * LDS * 2 + ks * 32), b[nt2][0], b[nt2][1], b[nt2][2], b[nt2][3]);
+#pragma unroll
+      for (int nt2 = 0; nt2 < 4; ++nt2) {
+        mma_bf16_16816(s[2 * nt2], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], b[nt2][0], b[nt2][1]);
+        mma_bf16_16816(s[2 * nt2 + 1], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], b[nt2][2], b[nt2][3]);
+      }
+#pragma unroll
+      for (int nt2 = 0; nt2 < 4; ++nt2) {
+        mma_bf16_16816(s[2 * nt2], ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], b[nt2][0], b[nt2][1]);
+        mma_bf16_16816(s[2 * nt2 + 1], ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], b[nt2][2], b[nt2][3]);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+      *reinterpret_cast<float4*>(spart + ((warp * 8 + nt) * 32 + lane) * 4) = make_float4(s[nt][0], s[nt][1], s[nt][2], s[nt][3]);
+    __syncthreads();
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const float4 a = *reinterpret_cast<const float4*>(spart + ((0 * 8 + nt) * 32 + lane) * 4);
+      const float4 b = *reinterpret_cast<const float4*>(spart + ((1 * 8 + nt) * 32 + lane) * 4);
+      const float4 cc = *reinterpret_cast<const float4*>(spart + ((2 * 8 + nt) * 32 + lane) * 4);
+      const float4 d = *reinterpret_cast<const float4*>(spart + ((3 * 8 + nt) * 32 + lane) * 4);
+      s[nt][0] = (a.x + b.x) + (cc.x + d.x);
+      s[nt][1] = (a.y + b.y) + (cc.y + d.y);
+      s[nt][2] = (a.z + b.z) + (cc.z + d.z);
+      s[nt][3] = (a.w + b.w) + (cc.w + d.w);
+    }
+    // ---- online softmax, rows g and g + 8, all 64 keys in this thread's quad ----
+    float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = nt * 8 + 2 * q4 + (e & 1);
+        if (key >= n) s[nt][e] = -INFINITY;
+        rmax[e >> 1] = fmaxf(rmax[e >> 1], s[nt][e]);
+      }
+    float corr[2], psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 1));
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 2));
+      const float mn = fmaxf(m_[r], rmax[r]);
+      corr[r] = expf(m_[r] - mn);
+      m_[r] = mn;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      s[nt][0] = expf(s[nt][0] - m_[0]);
+      s[nt][1] = expf(s[nt][1] - m_[0]);
+      s[nt][2] = expf(s[nt][2] - m_[1]);
+      s[nt][3] = expf(s[nt][3] - m_[1]);
+      psum[0] += s[nt][0] + s[nt][1];
+      psum[1] += s[nt][2] + s[nt][3];
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+      l_[r] = l_[r] * corr[r] + psum[r];
+    }
+    // ---- output dims of this warp: O = O * corr + P V ----
+#pragma unroll
+    for (int i = 0; i < NTW; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < LATENT_CHUNK / 16; ++kk) {
+      const uint32_t a0 = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]),
+                     a3 = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      const int key = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const uint32_t v_row = kb_s + (uint32_t)((key * LDS + dim_w + 8 * (lane >> 4)) * 2);
+#pragma unroll
+      for (int nd2 = 0; nd2 < NTW / 2; ++nd2) {
+        if (2 * nd2 < ntw) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(v_row + nd2 * 32, b0, b1, b2, b3);
+          mma_bf16_16816(o[2 * nd2], a0, a1, a2, a3, b0, b1);
+          mma_bf16_16816(o[2 * nd2 + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+    }
+  }
+  const float inv[2] = {1.f / l_[0], 1.f / l_[1]};
+#pragma unroll
+  for (int i = 0; i < NTW; ++i) {
+    if (i < ntw) {
+      const int dim = dim_w + i * 8 + 2 * q4;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int hh = h0 + g + 8 * r;
+        if (hh < heads)
+          *reinterpret_cast<uint32_t*>(out + ((long long)t * heads + hh) * R + dim) =
+              pack_bf16x2(o[i][2 * r] * inv[r], o[i][2 * r + 1] * inv[r]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // generalized delta rule.  One CTA per (sequence, head), thread j owns column j of the state S[key][value]
 // (kept in shared memory for the tokens of this step, loaded from / stored to the sequence's fp32 state
 // slot; a sequence whose first token this step is position 0 starts from zero, whatever the slot held).
@@ -743,28 +941,38 @@ __global__ void __launch_bounds__(D) delta_rule_reg_kernel(const T* __restrict__
 //             o_j = sum_q S[q] r[q]  -> raw[t, h*D + j] (fp32)
 //   finish    (CTA per token x head): out = raw / rms(raw) * out_norm * sigmoid(g)
 // ------------------------------------------------------------------------------------------------
+constexpr int DELTA_PREP_TOKENS = 16;  // tokens per CTA of the prepare kernel: the head's decay matrix is staged once
 template <typename T>
 __global__ void delta_prepare_kernel(const T* __restrict__ proj, int ldp, const T* __restrict__ w2,
                                      const float* __restrict__ w0, const float* __restrict__ a_bias, int heads, int D,
-                                     int Rk, float* __restrict__ vec) {
+                                     int Rk, int Tn, float* __restrict__ vec) {
   extern __shared__ float sm[];
-  float* zt = sm;        // [Rk]
-  float* red = zt + Rk;  // [32]
-  const int t = blockIdx.x, h = blockIdx.y, i = threadIdx.x, HD = heads * D, c = h * D + i;
-  const T* pr = proj + (long long)t * ldp;
-  for (int r = i; r < Rk; r += blockDim.x) zt[r] = tanhf(ldf(pr + 5 * HD + r));
-  const float kk = ldf(pr + HD + c);
-  const float ssk = block_sum(kk * kk, red);  // (its barriers also publish zt)
-  float z = w0[c];
-  const T* wr = w2 + (long long)c * Rk;
-  for (int r = 0; r < Rk; ++r) z = fmaf(ldf(wr + r), zt[r], z);
-  const float uu = kk / sqrtf(ssk + 1e-6f);
-  float* o = vec + ((long long)t * heads + h) * 5 * D;
-  o[i] = kk;
-  o[D + i] = uu;
-  o[2 * D + i] = sigmoidf_(ldf(pr + 4 * HD + c) + a_bias[c]) * uu;
-  o[3 * D + i] = expf(-0.6065306597126334f * sigmoidf_(z));
-  o[4 * D + i] = ldf(pr + c);
+  float* w2s = sm;                           // [Rk][D+1]
+  float* zt = w2s + (long long)Rk * (D + 1); // [Rk]
+  float* red = zt + Rk;                      // [32]
+  const int h = blockIdx.y, i = threadIdx.x, HD = heads * D, c = h * D + i;
+  for (int e = i; e < Rk * D; e += blockDim.x) {  // coalesced over the inner (rank) index of w2 [HD, Rk]
+    const int ch = e / Rk, r = e % Rk;
+    w2s[r * (D + 1) + ch] = ldf(w2 + (long long)(h * D + ch) * Rk + r);
+  }
+  const float w0c = w0[c], abc = a_bias[c];
+  const int t_end = min(Tn, (int)(blockIdx.x + 1) * DELTA_PREP_TOKENS);
+  for (int t = blockIdx.x * DELTA_PREP_TOKENS; t < t_end; ++t) {
+    const T* pr = proj + (long long)t * ldp;
+    __syncthreads();  // the previous token's zt has been read (first time: w2s is complete)
+    for (int r = i; r < Rk; r += blockDim.x) zt[r] = tanhf(ldf(pr + 5 * HD + r));
+    const float kk = ldf(pr + HD + c);
+    const float ssk = block_sum(kk * kk, red);  // (its barriers also publish zt)
+    float z = w0c;
+    for (int r = 0; r < Rk; ++r) z = fmaf(w2s[r * (D + 1) + i], zt[r], z);
+    const float uu = kk / sqrtf(ssk + 1e-6f);
+    float* o = vec + ((long long)t * heads + h) * 5 * D;
+    o[i] = kk;
+    o[D + i] = uu;
+    o[2 * D + i] = sigmoidf_(ldf(pr + 4 * HD + c) + abc) * uu;
+    o[3 * D + i] = expf(-0.6065306597126334f * sigmoidf_(z));
+    o[4 * D + i] = ldf(pr + c);
+  }
 }
 
 template <typename T, int D>
@@ -1208,16 +1416,36 @@ int b200q_latent_attn(const float* qa, const void* cache, const int32_t* block_t
   const size_t smem = (size_t)(8 * RP + 32 * (RP + 1)) * sizeof(float);
   B200Q_CHECK_ARG(smem <= 227 * 1024, "latent_attn: kv_rank + rot_dim = %d does not fit shared memory", RP);
   // bf16 caches whose sizes fit the tensor-core tiles (B200Q_LATENT_MMA=0: the scalar kernel everywhere)
-  static const bool use_mma = [] {
+  static const char mma_mode = [] {  // 0: scalar kernel everywhere, 1: never the register-query variant
     const char* v = getenv("B200Q_LATENT_MMA");
-    return !(v && v[0] == '0');
+    return v ? v[0] : '2';
   }();
+  const bool use_mma = mma_mode != '0';
   if (use_mma && dtype == B200Q_DTYPE_BF16 && kv_rank % 64 == 0 && kv_rank <= 512 && RP % 16 == 0 &&
       (reinterpret_cast<uintptr_t>(cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0) {
     const int LDS = RP + 8;
     const size_t sm2 = (size_t)(32 + 2 * LATENT_CHUNK) * LDS * 2 + 16 * LATENT_PLD * 2 + 128 * sizeof(float);
     if (sm2 <= 227 * 1024) {
       dim3 grid2(T_, (heads + 15) / 16);
+      // sizes whose key dimensions split evenly over the four warps keep the query in registers
+      const size_t sm3 = (size_t)2 * LATENT_CHUNK * LDS * 2 + 4 * 8 * 32 * 4 * sizeof(float);
+#define LATENT_MMA2(NTW, KS)                                                                                       \
+  do {                                                                                                            \
+    B200Q_CUDA(cudaFuncSetAttribute(latent_attn_mma2_kernel<NTW, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                    (int)sm3));                                                                   \
+    latent_attn_mma2_kernel<NTW, KS><<<grid2, 128, sm3, as_stream(stream)>>>(                                      \
+        qa, (const bf16*)cache, block_table, bt_stride, row_seq, positions, heads, kv_rank, rot_dim, block_size, \
+        window, scale, (bf16*)out);                                                                               \
+    B200Q_LAUNCH_CHECK();                                                                                         \
+    return B200Q_OK;                                                                                              \
+  } while (0)
+      if (RP % 64 == 0 && mma_mode != '1') {
+        if (kv_rank == 512 && RP == 576) LATENT_MMA2(16, 9);
+        if (kv_rank == 256 && RP == 320) LATENT_MMA2(8, 5);
+        if (kv_rank == 128 && RP == 192) LATENT_MMA2(4, 3);
+        if (kv_rank == 64 && RP == 128) LATENT_MMA2(2, 2);
+      }
+#undef LATENT_MMA2
 #define LATENT_MMA(NTW)                                                                                           \
   do {                                                                                                            \
     B200Q_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
@@ -1272,11 +1500,13 @@ int b200q_delta_rule(const void* proj, int ldp, const void* w2, const float* w0,
     float* raw = scratch + (long long)T_ * heads * D * 5;
     dim3 tg(T_, heads), sg(n_seqs, heads);
     cudaStream_t st = as_stream(stream);
-    const size_t psm = (size_t)(Rk + 32) * sizeof(float);
-    B200Q_CHECK_ARG(psm <= 48 * 1024, "delta_rule: decay rank %d too large", Rk);
+    const size_t psm = ((size_t)Rk * (D + 1) + Rk + 32) * sizeof(float);
+    B200Q_CHECK_ARG(psm <= 227 * 1024, "delta_rule: decay rank %d too large", Rk);
+    dim3 pg((T_ + DELTA_PREP_TOKENS - 1) / DELTA_PREP_TOKENS, heads);
 #define DELTA_SPLIT(TT)                                                                                           \
   do {                                                                                                            \
-    delta_prepare_kernel<TT><<<tg, D, psm, st>>>((const TT*)proj, ldp, (const TT*)w2, w0, a_bias, heads, D, Rk, vec); \
+    B200Q_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psm)); \
+    delta_prepare_kernel<TT><<<pg, D, psm, st>>>((const TT*)proj, ldp, (const TT*)w2, w0, a_bias, heads, D, Rk, T_, vec); \
     if (D == 32)                                                                                                  \
       delta_recur_kernel<TT, 32><<<sg, 32, 0, st>>>((const TT*)proj, ldp, vec, state, slot_stride, seq_desc, heads, raw); \
     else if (D == 64)                                                                                             \

@@ -206,7 +206,9 @@ def _latent_attn(cuda, qa, rows, pos, table, window, scale, R, P, bs=16, dtype=t
     return out.float().cpu()
 
 
-@pytest.mark.parametrize("window,H,R,P", [(0, 9, 64, 16), (70, 18, 128, 32), (64, 16, 192, 16), (5, 3, 64, 0)])
+@pytest.mark.parametrize("window,H,R,P", [(0, 9, 64, 16), (70, 18, 128, 32), (64, 16, 192, 16), (5, 3, 64, 0),
+                                          # (kv_rank + rot_dim) % 64 == 0: the variant with the query in registers
+                                          (70, 16, 64, 64), (0, 9, 128, 64), (33, 20, 256, 64), (0, 5, 512, 64)])
 def test_latent_attn_tensor_core_kernel(cuda, window, H, R, P):
     """the bf16 tensor-core kernel: random queries over hundreds of keys, and queries that single out one key
     (first key, chunk and page borders, window edge) — against the plain fp64 form on the same bf16 rows"""
