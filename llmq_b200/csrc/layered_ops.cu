@@ -527,8 +527,10 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const float* __res
     }
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
-      const float p0 = expf(s[nt][0] - m_[0]), p1 = expf(s[nt][1] - m_[0]);
-      const float p2 = expf(s[nt][2] - m_[1]), p3 = expf(s[nt][3] - m_[1]);
+      // the weights as the value product will see them (bf16): the row sum is taken over the same
+      // rounded values, so the weights of a row still add up to one
+      const float p0 = round_bf16(expf(s[nt][0] - m_[0])), p1 = round_bf16(expf(s[nt][1] - m_[0]));
+      const float p2 = round_bf16(expf(s[nt][2] - m_[1])), p3 = round_bf16(expf(s[nt][3] - m_[1]));
       psum[0] += p0 + p1;
       psum[1] += p2 + p3;
       const int col = 16 * warp + nt * 8 + 2 * q4;
@@ -731,10 +733,11 @@ __global__ void __launch_bounds__(128) latent_attn_mma2_kernel(const float* __re
     }
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-      s[nt][0] = expf(s[nt][0] - m_[0]);
-      s[nt][1] = expf(s[nt][1] - m_[0]);
-      s[nt][2] = expf(s[nt][2] - m_[1]);
-      s[nt][3] = expf(s[nt][3] - m_[1]);
+      // rounded to what the value product sees (bf16), so that a row's weights still add up to one
+      s[nt][0] = round_bf16(expf(s[nt][0] - m_[0]));
+      s[nt][1] = round_bf16(expf(s[nt][1] - m_[0]));
+      s[nt][2] = round_bf16(expf(s[nt][2] - m_[1]));
+      s[nt][3] = round_bf16(expf(s[nt][3] - m_[1]));
       psum[0] += s[nt][0] + s[nt][1];
       psum[1] += s[nt][2] + s[nt][3];
     }
