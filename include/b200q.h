@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200Q_VERSION 3
+#define B200Q_VERSION 4
 
 #define B200Q_OK 0
 #define B200Q_EINVAL (-1)   /* bad argument / unsupported shape            */
@@ -279,6 +279,81 @@ int b200q_moe_route(const float* logits_dev, int T, int E, int top, int32_t* idx
 int b200q_layer_sum(float* x_dev, const void* mix_dev, const void* f_dev, const void* expert_out_dev,
                     const int32_t* pair_pos_dev, const float* wts_dev, int top, const void* shared_out_dev,
                     const float* shared_gate_dev, int T, int W, int dtype, void* stream);
+/* moe_route with the scoring of the chosen experts selectable: score_mode 0 = softmax over the chosen logits,
+ * 1 = sigmoid of each chosen logit (not renormalised) */
+int b200q_moe_route_ex(const float* logits_dev, int T, int E, int top, int score_mode, int32_t* idx_dev,
+                       float* wts_dev, int32_t* group_off_dev, int32_t* perm_tok_dev, int32_t* pair_pos_dev,
+                       int32_t* tile_tab_dev, int32_t* n_tiles_dev, void* stream);
+
+/* ---- post-norm layers, carried convolutions, and mixers 3-5 (sequence_ops.cu) ------------------------------
+ * seq_desc / row_seq as in b200q_batch.  `state` arguments point at the op's own region inside slot 0 of the
+ * fp32 state pool; slot s is `slot_stride` floats further.  A sequence whose portion starts at position 0
+ * starts from zeros whatever its slot holds. */
+
+/* x[t,:] = table[ids[t],:] + pos_table[positions[t],:] into the fp32 residual (pos_table NULL: none) */
+int b200q_embed_pos_f32(const int32_t* ids_dev, const int32_t* prev_out_dev, const void* table_dev,
+                        const void* pos_table_dev, const int32_t* positions_dev, float* out_dev, int T, int W,
+                        int dtype, void* stream);
+/* grouped RMS norm of v = alpha * x + scale * add:  y = v / sqrt(mean_part(v^2) + eps) * w, the mean taken
+ * over each of `groups` equal consecutive parts of the row.  add (model dtype, may be NULL): row r, or with
+ * pair_pos the sum over k < top of rows pair_pos[r*top + k] (the routed experts' outputs).  scale NULL = 1.
+ * rows != NULL gathers x[rows[i]] into output row i.  y_f32 and / or y_t (model dtype) receive the result;
+ * y_f32 may be x itself. */
+int b200q_group_rmsnorm(const float* x_dev, const int32_t* rows_dev, const void* add_dev,
+                        const int32_t* pair_pos_dev, int top, const float* scale_dev, float alpha,
+                        const float* w_dev, int groups, float eps, float* y_f32_dev, void* y_t_dev, int n, int W,
+                        int dtype, void* stream);
+/* per-channel causal convolution over the tokens of each sequence's portion, continued from the last
+ * taps - 1 inputs the sequence left in its state slot:
+ *   y[t,c] = act( bias[c] + sum_j w[c,j] * in[t - taps + 1 + j, c] ) (+ in[t,c] if add_input)
+ * in: [T, ld_in] (fp32 if in_f32, else model dtype), w: fp32 [C, taps], out: [T, ld_out] (fp32 if out_f32).
+ * act 0 = none, 1 = SiLU.  The state is advanced by a second launch after the outputs are written. */
+int b200q_causal_conv(const void* in_dev, int ld_in, int in_f32, const float* w_dev, const float* bias_dev,
+                      int C, int taps, int act, int add_input, float* state_dev, long long slot_stride,
+                      const int32_t* seq_desc_dev, const int32_t* row_seq_dev, int n_seqs, void* out_dev,
+                      int ld_out, int out_f32, int T, int dtype, void* stream);
+/* gated delta rule.  qkv: fp32 [T, 2*kv_heads*dim + heads*vdim] = (q | k | v) after convolution and SiLU
+ * (q and k are normalised in place); ba: fp32 [T, 2*heads] = (beta logits | decay inputs), turned into
+ * (beta | g) in place; raw: fp32 scratch [T, heads*vdim]; gate: model dtype rows (ld_gate) of heads*vdim
+ * output gate logits.  Per head h (q/k head h / (heads/kv_heads)):
+ *   q <- q / sqrt(sum q^2 + 1e-6) * dim^-1/2,  k <- k / sqrt(sum k^2 + 1e-6),  beta = sigmoid(.),
+ *   g = exp(-exp(a_log[h]) * softplus(a + dt_bias[h]));  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;
+ *   o = S^T q;  out = o / sqrt(mean(o^2) + eps) * out_norm * silu(gate)
+ * state: fp32 [heads][dim][vdim] per slot. */
+int b200q_gated_delta(float* qkv_dev, float* ba_dev, float* raw_dev, const void* gate_dev, int ld_gate,
+                      const float* a_log_dev, const float* dt_bias_dev, const float* out_norm_dev,
+                      float* state_dev, long long slot_stride, const int32_t* seq_desc_dev, int n_seqs, int heads,
+                      int kv_heads, int dim, int vdim, float eps, void* out_dev, int T, int dtype, void* stream);
+/* chunk attention 1/2: proj row = [q (heads*dim) | k (kv_heads*dim) | ...];  qs[t,h,:] = q / rms(q) * w_qn *
+ * w_kn (fp32; the key norm's weight is carried by the query so that the cache holds the raw keys, which are
+ * also the values);  cache row slot_mapping[t] = k as projected (model dtype, [kv_heads*dim]) */
+int b200q_chunk_attn_prep(const void* proj_dev, int ldp, int heads, int kv_heads, int dim, const float* w_qn_dev,
+                          const float* w_kn_dev, const int32_t* slot_mapping_dev, float* qs_dev, void* cache_dev,
+                          int T, float eps, int dtype, void* stream);
+/* chunk attention 2/2: for token t at position p of its sequence, over keys j in [lo, p], lo = p - p % chunk
+ * (chunk 0: lo = 0):  s_j = (qs . k_j) / sqrt(mean(k_j^2) + eps) * scale;  s_j <- softcap tanh(s_j / softcap);
+ * s_j -= r1[h] * log(1 + r2[h] * (p - j));  w_j = exp(s_j) / (1 + sum exp(s));  out[t,h,:] = (sum_j w_j k_j) *
+ * sigmoid(gate[t,h,:]).  gate: model dtype rows with stride ld_gate. */
+int b200q_chunk_attn(const float* qs_dev, const void* cache_dev, const int32_t* block_table_dev, int bt_stride,
+                     const int32_t* row_seq_dev, const int32_t* positions_dev, int T, int heads, int kv_heads,
+                     int dim, int block_size, int chunk, float scale, float softcap, const float* r1_dev,
+                     const float* r2_dev, const void* gate_dev, int ld_gate, float eps, void* out_dev, int dtype,
+                     void* stream);
+/* selective scan.  x: model dtype [T, inner] (after convolution and SiLU); dt_raw: fp32 [T, inner] (before
+ * softplus, bias included); bc: model dtype rows (ld_bc) whose entries [b_off, b_off + N) are B and
+ * [b_off + N, b_off + 2N) are C; z: model dtype rows (ld_z); a_log: fp32 [inner, N]; d: fp32 [inner].
+ *   dt = softplus(dt_raw);  S[c,n] <- exp(dt_c * -exp(a_log[c,n])) S[c,n] + dt_c x_c B_n;
+ *   y_c = sum_n S[c,n] C_n + d_c x_c;  out = y * silu(z).     state: fp32 [inner][N] per slot. */
+int b200q_selective_scan(const void* x_dev, const float* dt_raw_dev, const void* bc_dev, int ld_bc, int b_off,
+                         const void* z_dev, int ld_z, const float* a_log_dev, const float* d_dev, float* state_dev,
+                         long long slot_stride, const int32_t* seq_desc_dev, int n_seqs, int inner, int N,
+                         void* out_dev, int dtype, void* stream);
+/* routed experts whose weight scales the INPUT: dst[pair_pos[p], :] = src[p / top, :] * wts[p] for every
+ * (token, choice) pair p < T*top (rows land in expert order for the grouped linear) */
+int b200q_scatter_scaled_rows(const void* src_dev, const int32_t* pair_pos_dev, const float* wts_dev, int top,
+                              void* dst_dev, int T, int W, int dtype, void* stream);
+/* gated unit: gate_up row = [g (F) | u (F)]; y = silu(g) * u */
+int b200q_silu_glu(const void* gate_up_dev, void* y_dev, int64_t rows, int F, int dtype, void* stream);
 int b200q_argmax_f32(const float* logits_dev, int32_t* ids_dev, int B, int V, void* stream);
 int b200q_f32_to_bf16(const float* in_dev, void* out_dev, int64_t n, void* stream);
 int b200q_copy_f32(const float* in_dev, float* out_dev, int64_t n, void* stream);
@@ -315,6 +390,14 @@ typedef struct b200q_model_config {
   int32_t max_logit_rows; /* rows of the fp32 logits buffer (0 = max_seqs); a replayed step may ask for the
                              logits of any of its rows                                                     */
   int32_t state_slots;    /* recurrent-state slots (one per live sequence); 0 = max_seqs                    */
+  /* form of a layer (layered architectures); all zero = parallel pre-norm layers                            */
+  int32_t layer_form;     /* B200Q_FORM_PARALLEL | B200Q_FORM_POSTNORM                                       */
+  int32_t norm_groups;    /* post-norm form: the RMS norms (layers and final) are taken over this many equal
+                             consecutive parts of a row; 0 / 1 = the whole row                               */
+  float residual_alpha;   /* post-norm form: x <- norm(alpha * x + scale * sublayer(x))                      */
+  int32_t input_taps;     /* post-norm form: every sublayer reads h + conv(h), a per-channel causal
+                             convolution over time with this many taps ("canon1" / "canon2"); 0 = reads x    */
+  int32_t learned_pos;    /* 1: a learned position table "pos" [>= max_pos, W] is added to the embedding     */
 } b200q_model_config;
 
 #define B200Q_ARCH_LLAMA 0
@@ -322,15 +405,34 @@ typedef struct b200q_model_config {
 /* Ramopel: a layered decoder.  Every layer is  x <- x + mixer(norm1 x) + ff(norm2 x)  with the residual
  * x in fp32; the mixer and the feed-forward of each layer are chosen by its b200q_layer_desc. */
 #define B200Q_ARCH_RAMOPEL 2
+/* Noridra: a layered decoder in post-norm form.  Every layer is
+ *   x <- norm1(alpha x + ls1 * mixer(x + conv1 x));  x <- norm2(alpha x + ls2 * ff(x + conv2 x))
+ * with grouped RMS norms, per-channel layer scales ls and causal input convolutions whose last inputs are
+ * carried in the sequence's state slot; mixers and feed-forwards again come from b200q_layer_desc. */
+#define B200Q_ARCH_NORIDRA 3
+
+#define B200Q_FORM_PARALLEL 0  /* x <- x + mixer(norm1 x) + ff(norm2 x)                                  */
+#define B200Q_FORM_POSTNORM 1  /* x <- norm1(alpha x + ls1 mixer(x~)); x <- norm2(alpha x + ls2 ff(x~)) */
 
 #define B200Q_DTYPE_BF16 0
 #define B200Q_DTYPE_F32 1
 
 #define B200Q_MIXER_LATENT_ATTN 1   /* low-rank (latent) queries and keys/values, sliding window, paged latent cache */
 #define B200Q_MIXER_GENERAL_DELTA 2 /* generalized delta-rule recurrence, fp32 state per (sequence, head)            */
+/* gated delta rule: per head a [dim x vdim] fp32 state, S <- g S + k (beta (v - S^T k))^T, o = S^T q; q, k
+ * (kv_heads x dim) and v (heads x vdim) pass a short causal convolution + SiLU, q and k are unit vectors    */
+#define B200Q_MIXER_GATED_DELTA 3
+/* grouped-query attention over a paged cache of raw keys that also serve as values; per-head RMS norm of
+ * queries and keys, soft-capped scores, a logarithmic distance penalty per head, visibility limited to the
+ * query's own chunk of `chunk` positions, a softmax with a silent sink (denominator + 1), a sigmoid gate   */
+#define B200Q_MIXER_CHUNK_ATTN 4
+/* selective scan: per channel a [state_dim] fp32 state, S <- exp(dt A) S + dt x B, y = S.C + D x           */
+#define B200Q_MIXER_SELECTIVE_SCAN 5
 #define B200Q_FF_NONE 0
 #define B200Q_FF_POLYNORM 1         /* down(PolyNorm(up h))                                                          */
 #define B200Q_FF_MOE 2              /* top-k of clamped gated experts + an optional gated shared expert              */
+#define B200Q_FF_MOE_SIGMOID 3      /* top-k by sigmoid score, weights = the scores (not renormalised) applied to the
+                                       expert's INPUT; expert = down(silu(gate h) * up h)                            */
 
 typedef struct b200q_layer_desc {
   int32_t mixer;        /* B200Q_MIXER_*                                                               */
@@ -353,6 +455,14 @@ typedef struct b200q_layer_desc {
   float expert_limit;
   int32_t shared_dim;   /* moe: ff size of the shared expert, 0 = none                                  */
   float shared_limit;
+  /* mixers 3-5 (zero elsewhere) */
+  int32_t kv_heads;     /* gated delta / chunk attention: heads of q and k (delta) or of k (attention)    */
+  int32_t conv_taps;    /* gated delta / selective scan: taps of the mixer's short convolution            */
+  float softcap;        /* chunk attention: scores <- softcap * tanh(scores / softcap); 0 = off           */
+  int32_t chunk;        /* chunk attention: i sees j <= i with floor(i/chunk) == floor(j/chunk); 0 = all  */
+  int32_t inner;        /* selective scan: channels                                                       */
+  int32_t state_dim;    /* selective scan: state size per channel                                         */
+  int32_t dt_rank;      /* selective scan: rank of the step-size projection                               */
 } b200q_layer_desc;
 
 typedef struct b200q_model* b200q_model_t;

@@ -25,7 +25,14 @@ int logit_rows(const b200q_model_config& c) { return std::max(c.max_logit_rows, 
 
 int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
   B200Q_CHECK_ARG(c && L, "layered config is null");
-  B200Q_CHECK_ARG(c->arch == B200Q_ARCH_RAMOPEL, "create_layered: arch=%d is not a layered architecture", c->arch);
+  B200Q_CHECK_ARG(c->arch == B200Q_ARCH_RAMOPEL || c->arch == B200Q_ARCH_NORIDRA,
+                  "create_layered: arch=%d is not a layered architecture", c->arch);
+  B200Q_CHECK_ARG(c->layer_form == B200Q_FORM_PARALLEL || c->layer_form == B200Q_FORM_POSTNORM, "layer_form=%d unknown",
+                  c->layer_form);
+  B200Q_CHECK_ARG(c->norm_groups >= 0 && (c->norm_groups <= 1 || c->hidden % c->norm_groups == 0) &&
+                      c->input_taps >= 0 && c->input_taps <= 16,
+                  "bad norm groups (%d must divide the width %d) or input taps (%d, at most 16)", c->norm_groups,
+                  c->hidden, c->input_taps);
   B200Q_CHECK_ARG(c->dtype == B200Q_DTYPE_BF16 || c->dtype == B200Q_DTYPE_F32, "dtype=%d unknown", c->dtype);
   B200Q_CHECK_ARG(c->hidden > 0 && c->vocab > 0 && c->n_layers > 0 && c->max_tokens > 0 && c->max_seqs > 0 &&
                       c->max_pos > 0 && c->block_size > 0 && c->rms_eps > 0.f,
@@ -47,11 +54,28 @@ int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
     } else if (d.mixer == B200Q_MIXER_GENERAL_DELTA) {
       B200Q_CHECK_ARG(d.heads > 0 && d.dim > 0 && d.dim <= 1024 && d.decay_rank > 0,
                       "layer %d: bad delta-rule sizes", i);
+    } else if (d.mixer == B200Q_MIXER_GATED_DELTA) {
+      B200Q_CHECK_ARG(d.heads > 0 && d.kv_heads > 0 && d.heads % d.kv_heads == 0 && d.dim > 0 && d.dim <= 256 &&
+                          d.vdim > 0 && d.vdim <= 1024 && d.conv_taps >= 1 && d.conv_taps <= 16,
+                      "layer %d: bad gated-delta sizes (dim <= 256, vdim <= 1024, taps <= 16, kv_heads divides heads)", i);
+    } else if (d.mixer == B200Q_MIXER_CHUNK_ATTN) {
+      B200Q_CHECK_ARG(d.heads > 0 && d.kv_heads > 0 && d.heads % d.kv_heads == 0 && d.dim > 0 && d.dim <= 512 &&
+                          d.vdim == d.dim && d.chunk >= 0 && d.softcap >= 0.f,
+                      "layer %d: bad chunk-attention sizes (dim <= 512; the values are the keys, so vdim == dim)", i);
+    } else if (d.mixer == B200Q_MIXER_SELECTIVE_SCAN) {
+      B200Q_CHECK_ARG(d.inner > 0 && d.state_dim > 0 && d.state_dim <= 256 && d.dt_rank > 0 && d.conv_taps >= 1 &&
+                          d.conv_taps <= 16,
+                      "layer %d: bad selective-scan sizes (state <= 256, taps <= 16)", i);
     } else {
       set_error("layer %d: unknown mixer %d", i, d.mixer);
       return B200Q_EINVAL;
     }
-    if (d.ff == B200Q_FF_POLYNORM) {
+    if (d.ff == B200Q_FF_MOE_SIGMOID) {
+      B200Q_CHECK_ARG(d.ff_dim > 0 && d.n_experts > 0 && d.n_experts <= 4096 && d.top_k > 0 && d.top_k <= 32 &&
+                          d.top_k <= d.n_experts,
+                      "layer %d: bad mixture sizes (experts <= 4096, top <= 32)", i);
+      B200Q_CHECK_ARG(c->layer_form == B200Q_FORM_POSTNORM, "layer %d: this mixture belongs to the post-norm form", i);
+    } else if (d.ff == B200Q_FF_POLYNORM) {
       B200Q_CHECK_ARG(d.ff_dim > 0, "layer %d: bad ff size", i);
     } else if (d.ff == B200Q_FF_MOE) {
       B200Q_CHECK_ARG(d.ff_dim > 0 && d.n_experts > 0 && d.n_experts <= 4096 && d.top_k > 0 && d.top_k <= 32 &&
@@ -67,7 +91,7 @@ int check_layered(const b200q_model_config* c, const b200q_layer_desc* L) {
 // widest use of every workspace buffer over the layers
 struct Widths {
   int64_t proj = 1, cq = 1, q = 1, qa = 1, olat = 1, attn = 1, ffh = 1, ffa = 1, experts = 1, pairs = 1, egu = 1,
-          eact = 1, delta = 0;
+          eact = 1, delta = 0, cvf = 0, baf = 0, dtr = 0, xc = 0, xp = 0;
   bool moe = false, shared = false;
 };
 Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_layer>& Ls) {
@@ -82,12 +106,35 @@ Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_la
       w.qa = std::max<int64_t>(w.qa, (int64_t)d.heads * RP);
       w.olat = std::max<int64_t>(w.olat, (int64_t)d.heads * d.kv_rank);
       w.attn = std::max<int64_t>(w.attn, (int64_t)d.heads * d.vdim);
-    } else {
+    } else if (d.mixer == B200Q_MIXER_GENERAL_DELTA) {
       w.proj = std::max<int64_t>(w.proj, 5 * (int64_t)d.heads * d.dim + d.decay_rank);
       w.attn = std::max<int64_t>(w.attn, (int64_t)d.heads * d.dim);
       w.delta = std::max<int64_t>(w.delta, (int64_t)d.heads * d.dim);
+    } else if (d.mixer == B200Q_MIXER_GATED_DELTA) {
+      const int64_t GD = (int64_t)d.kv_heads * d.dim, HV = (int64_t)d.heads * d.vdim;
+      w.proj = std::max<int64_t>(w.proj, 2 * GD + 2 * HV);
+      w.cvf = std::max<int64_t>(w.cvf, 2 * GD + 2 * HV);  // convolved q|k|v and, behind them, the raw outputs
+      w.baf = std::max<int64_t>(w.baf, 2 * (int64_t)d.heads);
+      w.attn = std::max<int64_t>(w.attn, HV);
+    } else if (d.mixer == B200Q_MIXER_CHUNK_ATTN) {
+      const int64_t HD = (int64_t)d.heads * d.dim;
+      w.proj = std::max<int64_t>(w.proj, 2 * HD + (int64_t)d.kv_heads * d.dim);
+      w.qa = std::max<int64_t>(w.qa, HD);
+      w.attn = std::max<int64_t>(w.attn, HD);
+    } else if (d.mixer == B200Q_MIXER_SELECTIVE_SCAN) {
+      w.proj = std::max<int64_t>(w.proj, 2 * (int64_t)d.inner);
+      w.xc = std::max<int64_t>(w.xc, d.inner);
+      w.xp = std::max<int64_t>(w.xp, d.dt_rank + 2 * (int64_t)d.state_dim);
+      w.dtr = std::max<int64_t>(w.dtr, d.inner);
+      w.attn = std::max<int64_t>(w.attn, d.inner);
     }
-    if (d.ff == B200Q_FF_POLYNORM) {
+    if (d.ff == B200Q_FF_MOE_SIGMOID) {
+      w.moe = true;
+      w.experts = std::max<int64_t>(w.experts, d.n_experts);
+      w.pairs = std::max<int64_t>(w.pairs, d.top_k);
+      w.egu = std::max<int64_t>(w.egu, (int64_t)d.top_k * 2 * d.ff_dim);
+      w.eact = std::max<int64_t>(w.eact, (int64_t)d.top_k * d.ff_dim);
+    } else if (d.ff == B200Q_FF_POLYNORM) {
       w.ffh = std::max<int64_t>(w.ffh, d.ff_dim);
       w.ffa = std::max<int64_t>(w.ffa, d.ff_dim);
     } else if (d.ff == B200Q_FF_MOE) {
@@ -130,6 +177,11 @@ int64_t layout(b200q_model* m, uint8_t* base) {
   y->olat = take(T * w.olat * es);
   y->attn = take(T * w.attn * es);
   y->dscr = (float*)take(w.delta ? T * w.delta * 6 * 4 : 1);
+  y->cvf = (float*)take(w.cvf ? T * w.cvf * 4 : 1);
+  y->baf = (float*)take(w.baf ? T * w.baf * 4 : 1);
+  y->dtr = (float*)take(w.dtr ? T * w.dtr * 4 : 1);
+  y->xc = take(w.xc ? T * w.xc * es : 1);
+  y->xp = take(w.xp ? T * w.xp * es : 1);
   y->ffh = take(T * w.ffh * es);
   y->ffa = take(T * w.ffa * es);
   y->rlog = (float*)take(T * w.experts * 4);
@@ -189,10 +241,33 @@ int layered_create(const b200q_model_config* cfg, const b200q_layer_desc* layers
           return B200Q_ECUDA;
         }
       }
-    } else {
+    } else if (l.d.mixer == B200Q_MIXER_GENERAL_DELTA) {
       l.state_off = m->lay->state_slot_floats;
       m->lay->state_slot_floats += (int64_t)l.d.heads * l.d.dim * l.d.dim;
+    } else if (l.d.mixer == B200Q_MIXER_GATED_DELTA) {
+      l.state_off = m->lay->state_slot_floats;
+      m->lay->state_slot_floats += (int64_t)l.d.heads * l.d.dim * l.d.vdim;
+      l.conv_off = m->lay->state_slot_floats;
+      m->lay->state_slot_floats += (int64_t)(l.d.conv_taps - 1) * (2 * l.d.kv_heads * l.d.dim + l.d.heads * l.d.vdim);
+    } else if (l.d.mixer == B200Q_MIXER_CHUNK_ATTN) {
+      l.cache_block_off = m->lay->kv_block_bytes;
+      m->lay->kv_block_bytes += (int64_t)cfg->block_size * l.d.kv_heads * l.d.dim * es;
+    } else if (l.d.mixer == B200Q_MIXER_SELECTIVE_SCAN) {
+      l.state_off = m->lay->state_slot_floats;
+      m->lay->state_slot_floats += (int64_t)l.d.inner * l.d.state_dim;
+      l.conv_off = m->lay->state_slot_floats;
+      m->lay->state_slot_floats += (int64_t)(l.d.conv_taps - 1) * l.d.inner;
     }
+    if (cfg->layer_form == B200Q_FORM_POSTNORM && cfg->input_taps > 1) {
+      // the last inputs of the two sublayers' input convolutions travel with the sequence
+      l.canon1_off = m->lay->state_slot_floats;
+      m->lay->state_slot_floats += (int64_t)(cfg->input_taps - 1) * cfg->hidden;
+      if (l.d.ff != B200Q_FF_NONE) {
+        l.canon2_off = m->lay->state_slot_floats;
+        m->lay->state_slot_floats += (int64_t)(cfg->input_taps - 1) * cfg->hidden;
+      }
+    }
+    m->lay->state_slot_floats = (m->lay->state_slot_floats + 3) & ~(int64_t)3;  // regions stay 16-byte aligned
   }
   *out = m;
   return B200Q_OK;
@@ -230,6 +305,13 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
   if (!strcmp(name, "embed")) { if ((rc = expect(c.vocab, W))) return rc; m->embed = p; return B200Q_OK; }
   if (!strcmp(name, "final_norm")) { if ((rc = expect(1, W))) return rc; m->final_norm = p; return B200Q_OK; }
   if (!strcmp(name, "lm_head")) { if ((rc = expect(c.vocab, W))) return rc; m->lm_head = p; return B200Q_OK; }
+  if (!strcmp(name, "pos")) {
+    B200Q_CHECK_ARG(c.learned_pos && cols == W && rows >= c.max_pos, "weight pos has shape [%lld,%lld], expected [>= %d,%lld]",
+                    (long long)rows, (long long)cols, c.max_pos, (long long)W);
+    m->lay->pos = p;
+    m->lay->pos_rows = rows;
+    return B200Q_OK;
+  }
   int li = -1;
   char field[48] = {0};
   if (sscanf(name, "layers.%d.%47s", &li, field) != 2 || li < 0 || li >= c.n_layers) {
@@ -247,7 +329,41 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
   }
   FIELD("norm1", l.norm1, 1, W)
   if (d.ff != B200Q_FF_NONE) FIELD("norm2", l.norm2, 1, W)
-  if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
+  if (c.layer_form == B200Q_FORM_POSTNORM) {
+    FIELD("ls1", l.ls1, 1, W)
+    if (d.ff != B200Q_FF_NONE) FIELD("ls2", l.ls2, 1, W)
+    if (c.input_taps > 0) {
+      FIELD("canon1", l.canon1, 1, W * c.input_taps)
+      if (d.ff != B200Q_FF_NONE) FIELD("canon2", l.canon2, 1, W * c.input_taps)
+    }
+  }
+  if (d.mixer == B200Q_MIXER_GATED_DELTA) {
+    const int64_t GD = (int64_t)d.kv_heads * d.dim, HV = (int64_t)d.heads * d.vdim;
+    FIELD("mix.proj", l.proj, 2 * GD + 2 * HV, W)
+    FIELD("mix.ba", l.ba, 2 * d.heads, W)
+    FIELD("mix.conv", l.conv_w, 1, (2 * GD + HV) * d.conv_taps)
+    FIELD("mix.a_log", l.a_log, 1, d.heads)
+    FIELD("mix.dt_bias", l.dt_bias, 1, d.heads)
+    FIELD("mix.out_norm", l.out_norm, 1, d.vdim)
+    FIELD("mix.o", l.o, W, HV)
+  } else if (d.mixer == B200Q_MIXER_CHUNK_ATTN) {
+    FIELD("mix.proj", l.proj, 2 * HD + (int64_t)d.kv_heads * d.dim, W)
+    FIELD("mix.q_norm", l.q_norm, 1, d.dim)
+    FIELD("mix.k_norm", l.kv_norm, 1, d.dim)
+    FIELD("mix.r1", l.r1, 1, d.heads)
+    FIELD("mix.r2", l.r2, 1, d.heads)
+    FIELD("mix.o", l.o, W, HD)
+  } else if (d.mixer == B200Q_MIXER_SELECTIVE_SCAN) {
+    FIELD("mix.proj", l.proj, 2 * d.inner, W)
+    FIELD("mix.conv", l.conv_w, 1, (int64_t)d.inner * d.conv_taps)
+    FIELD("mix.conv_b", l.conv_b, 1, d.inner)
+    FIELD("mix.x", l.x_proj, d.dt_rank + 2 * d.state_dim, d.inner)
+    FIELD("mix.dt", l.dt_proj, d.inner, d.dt_rank)
+    FIELD("mix.dt_b", l.dt_b, 1, d.inner)
+    FIELD("mix.a_log", l.a_log, 1, (int64_t)d.inner * d.state_dim)
+    FIELD("mix.d", l.dvec, 1, d.inner)
+    FIELD("mix.o", l.o, W, d.inner)
+  } else if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
     const int64_t RP = d.kv_rank + d.rot_dim;
     FIELD("mix.down", l.down, d.q_rank + (d.kv_from < 0 ? RP : 0), W)
     FIELD("mix.q_norm", l.q_norm, 1, d.q_rank)
@@ -256,7 +372,7 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
     FIELD("mix.uk_t", l.uk_t, (int64_t)d.heads * d.kv_rank, d.dim)
     FIELD("mix.uv", l.uv, (int64_t)d.heads * d.vdim, d.kv_rank)
     FIELD("mix.o", l.o, W, (int64_t)d.heads * d.vdim)
-  } else {
+  } else if (d.mixer == B200Q_MIXER_GENERAL_DELTA) {
     FIELD("mix.proj", l.proj, 5 * HD + d.decay_rank, W)
     FIELD("mix.w2", l.w2, HD, d.decay_rank)
     FIELD("mix.w0", l.w0, 1, HD)
@@ -264,7 +380,11 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
     FIELD("mix.out_norm", l.out_norm, 1, HD)
     FIELD("mix.o", l.o, W, HD)
   }
-  if (d.ff == B200Q_FF_POLYNORM) {
+  if (d.ff == B200Q_FF_MOE_SIGMOID) {
+    FIELD("mlp.router", l.router, d.n_experts, W)
+    FIELD("mlp.experts_gate_up", l.experts_gate_up, (int64_t)d.n_experts * 2 * d.ff_dim, W)
+    FIELD("mlp.experts_down", l.experts_down, (int64_t)d.n_experts * W, d.ff_dim)
+  } else if (d.ff == B200Q_FF_POLYNORM) {
     FIELD("mlp.up", l.up, d.ff_dim, W)
     FIELD("mlp.act", l.act, 1, 4)
     FIELD("mlp.down", l.ff_down, W, d.ff_dim)
@@ -285,8 +405,8 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
 }
 
 static int check_bound(b200q_model* m) {
-  if (!m->embed || !m->final_norm || !m->lm_head || !m->ws) {
-    set_error("forward: model not fully bound (embed/final_norm/lm_head/workspace)");
+  if (!m->embed || !m->final_norm || !m->lm_head || !m->ws || (m->cfg.learned_pos && !m->lay->pos)) {
+    set_error("forward: model not fully bound (embed/pos/final_norm/lm_head/workspace)");
     return B200Q_ESTATE;
   }
   bool need_kv = false, need_state = false;
@@ -294,13 +414,28 @@ static int check_bound(b200q_model* m) {
     const b200q_layered_layer& l = m->lay->layers[i];
     const b200q_layer_desc& d = l.d;
     bool ok = l.norm1 && l.o && (d.ff == B200Q_FF_NONE || l.norm2);
+    if (m->cfg.layer_form == B200Q_FORM_POSTNORM) {
+      ok = ok && l.ls1 && (d.ff == B200Q_FF_NONE || l.ls2);
+      if (m->cfg.input_taps > 0) ok = ok && l.canon1 && (d.ff == B200Q_FF_NONE || l.canon2);
+      if (m->cfg.input_taps > 1) need_state = true;
+    }
     if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
       need_kv = true;
       ok = ok && l.down && l.q_norm && (d.kv_from >= 0 || l.kv_norm) && l.uq && l.uk_t && l.uv;
-    } else {
+    } else if (d.mixer == B200Q_MIXER_GENERAL_DELTA) {
       need_state = true;
       ok = ok && l.proj && l.w2 && l.w0 && l.a_bias && l.out_norm;
+    } else if (d.mixer == B200Q_MIXER_GATED_DELTA) {
+      need_state = true;
+      ok = ok && l.proj && l.ba && l.conv_w && l.a_log && l.dt_bias && l.out_norm;
+    } else if (d.mixer == B200Q_MIXER_CHUNK_ATTN) {
+      need_kv = true;
+      ok = ok && l.proj && l.q_norm && l.kv_norm && l.r1 && l.r2;
+    } else if (d.mixer == B200Q_MIXER_SELECTIVE_SCAN) {
+      need_state = true;
+      ok = ok && l.proj && l.conv_w && l.conv_b && l.x_proj && l.dt_proj && l.dt_b && l.a_log && l.dvec;
     }
+    if (d.ff == B200Q_FF_MOE_SIGMOID) ok = ok && l.router && l.experts_gate_up && l.experts_down;
     if (d.ff == B200Q_FF_POLYNORM) ok = ok && l.up && l.act && l.ff_down;
     if (d.ff == B200Q_FF_MOE)
       ok = ok && l.router && l.router_bias && l.experts_gate_up && l.experts_down &&
@@ -350,17 +485,19 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
       b200q_linear((Aptr), (lda), (Wptr), (bias), (Cptr), (ldc), T, (N), (K), dt, (f32), stream))
   const int EW = B200Q_PROF_ELEMENTWISE;
 
-  TRY(EW, (double)T * W * (es + 4),
-      b200q_embed_f32(b->token_ids, b->prev_out_ids, m->embed, y->x, T, W, c.embed_scale > 0.f ? c.embed_scale : 1.f,
-                      dt, stream));
-  for (int li = 0; li < c.n_layers; ++li) {
-    const b200q_layered_layer& l = y->layers[li];
+  const bool post = c.layer_form == B200Q_FORM_POSTNORM;
+  const int groups = c.norm_groups > 0 ? c.norm_groups : 1;
+  if (c.learned_pos)
+    TRY(EW, (double)T * W * (2 * es + 4),
+        b200q_embed_pos_f32(b->token_ids, b->prev_out_ids, m->embed, y->pos, b->positions, y->x, T, W, dt, stream));
+  else
+    TRY(EW, (double)T * W * (es + 4),
+        b200q_embed_f32(b->token_ids, b->prev_out_ids, m->embed, y->x, T, W, c.embed_scale > 0.f ? c.embed_scale : 1.f,
+                        dt, stream));
+
+  // ---- the mixers: read y->h1 [T, W] (model dtype), write y->mix [T, W] ----
+  auto run_mixer = [&](const b200q_layered_layer& l) -> int {
     const b200q_layer_desc& d = l.d;
-    const bool has_ff = d.ff != B200Q_FF_NONE;
-    TRY(EW, (double)T * W * (4 + 2 * es),
-        b200q_centered_rmsnorm(y->x, nullptr, l.norm1, l.norm2, y->h1, has_ff ? y->h2 : nullptr, T, W, c.rms_eps, dt,
-                               stream));
-    // ---- mixer ----
     if (d.mixer == B200Q_MIXER_LATENT_ATTN) {
       const int R = d.kv_rank, P = d.rot_dim, RP = R + P, H = d.heads, QD = d.dim + P;
       const bool own = d.kv_from < 0;
@@ -387,7 +524,7 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
           b200q_linear_batched(y->olat, H * R, R, l.uv, (long long)d.vdim * R, y->attn, H * d.vdim, d.vdim, T, d.vdim, R,
                                H, dt, 0, stream));
       LIN(y->attn, H * d.vdim, l.o, nullptr, y->mix, W, W, H * d.vdim, 0);
-    } else {
+    } else if (d.mixer == B200Q_MIXER_GENERAL_DELTA) {
       const int HD = d.heads * d.dim, NP = 5 * HD + d.decay_rank;
       LIN(y->h1, W, l.proj, nullptr, y->proj, NP, NP, W, 0);
       TRY(B200Q_PROF_PREFILL_ATTN, 0.0,
@@ -396,7 +533,106 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
                            y->attn, dt, T > b->n_rows ? y->dscr : nullptr /* portions of prompts: three launches */, T,
                            stream));
       LIN(y->attn, HD, l.o, nullptr, y->mix, W, W, HD, 0);
+    } else if (d.mixer == B200Q_MIXER_GATED_DELTA) {
+      const int H = d.heads, GD = d.kv_heads * d.dim, HV = H * d.vdim, NC = 2 * GD + HV, NP = NC + HV;
+      LIN(y->h1, W, l.proj, nullptr, y->proj, NP, NP, W, 0);          // [q | k | v | gate]
+      LIN(y->h1, W, l.ba, nullptr, y->baf, 2 * H, 2 * H, W, 1);       // [beta | decay input], fp32
+      TRY(EW, (double)T * NC * (es + 4),
+          b200q_causal_conv(y->proj, NP, 0, l.conv_w, nullptr, NC, d.conv_taps, 1, 0, y->state + l.conv_off,
+                            y->state_slot_floats, b->seq_desc, b->row_seq, b->n_rows, y->cvf, NC, 1, T, dt, stream));
+      uint8_t* gate = (uint8_t*)y->proj + (size_t)NC * es;
+      TRY(B200Q_PROF_PREFILL_ATTN, 8.0 * b->n_rows * H * (double)d.dim * d.vdim,
+          b200q_gated_delta(y->cvf, y->baf, y->cvf + (int64_t)T * NC, gate, NP, l.a_log, l.dt_bias, l.out_norm,
+                            y->state + l.state_off, y->state_slot_floats, b->seq_desc, b->n_rows, H, d.kv_heads, d.dim,
+                            d.vdim, c.rms_eps, y->attn, T, dt, stream));
+      LIN(y->attn, HV, l.o, nullptr, y->mix, W, W, HV, 0);
+    } else if (d.mixer == B200Q_MIXER_CHUNK_ATTN) {
+      const int H = d.heads, G = d.kv_heads, D = d.dim, HD = H * D, NP = 2 * HD + G * D;
+      uint8_t* cache = m->kv + m->num_blocks * l.cache_block_off;
+      LIN(y->h1, W, l.proj, nullptr, y->proj, NP, NP, W, 0);          // [q | k | gate]
+      TRY(EW, (double)T * ((HD + G * D) * es + HD * 4 + G * D * es),
+          b200q_chunk_attn_prep(y->proj, NP, H, G, D, l.q_norm, l.kv_norm, b->slot_mapping, y->qa, cache, T, c.rms_eps, dt,
+                                stream));
+      uint8_t* gate = (uint8_t*)y->proj + (size_t)(HD + G * D) * es;
+      TRY(B200Q_PROF_DECODE_ATTN, (double)b->sum_ctx_dec * G * D * es,
+          b200q_chunk_attn(y->qa, cache, b->block_table, b->bt_stride, b->row_seq, b->positions, T, H, G, D, c.block_size,
+                           d.chunk, d.attn_scale, d.softcap, l.r1, l.r2, gate, NP, c.rms_eps, y->attn, dt, stream));
+      LIN(y->attn, HD, l.o, nullptr, y->mix, W, W, HD, 0);
+    } else {  // B200Q_MIXER_SELECTIVE_SCAN
+      const int I = d.inner, N = d.state_dim, R = d.dt_rank, NX = R + 2 * N;
+      LIN(y->h1, W, l.proj, nullptr, y->proj, 2 * I, 2 * I, W, 0);    // [x | z]
+      TRY(EW, 2.0 * T * I * es,
+          b200q_causal_conv(y->proj, 2 * I, 0, l.conv_w, l.conv_b, I, d.conv_taps, 1, 0, y->state + l.conv_off,
+                            y->state_slot_floats, b->seq_desc, b->row_seq, b->n_rows, y->xc, I, 0, T, dt, stream));
+      LIN(y->xc, I, l.x_proj, nullptr, y->xp, NX, NX, I, 0);          // [dt | B | C]
+      LIN(y->xp, NX, l.dt_proj, l.dt_b, y->dtr, I, I, R, 1);          // step sizes before softplus, fp32
+      uint8_t* z = (uint8_t*)y->proj + (size_t)I * es;
+      TRY(B200Q_PROF_PREFILL_ATTN, 8.0 * b->n_rows * (double)I * N,
+          b200q_selective_scan(y->xc, y->dtr, y->xp, NX, R, z, 2 * I, l.a_log, l.dvec, y->state + l.state_off,
+                               y->state_slot_floats, b->seq_desc, b->n_rows, I, N, y->attn, dt, stream));
+      LIN(y->attn, I, l.o, nullptr, y->mix, W, W, I, 0);
     }
+    return B200Q_OK;
+  };
+
+  // ---- sigmoid-routed experts of the post-norm form: read y->h2, leave the pairs' outputs in y->eout ----
+  auto run_moe_sigmoid = [&](const b200q_layered_layer& l) -> int {
+    const b200q_layer_desc& d = l.d;
+    const int E = d.n_experts, K = d.top_k, F = d.ff_dim, P = T * K;
+    LIN(y->h2, W, l.router, nullptr, y->rlog, E, E, W, 1);
+    TRY(EW, (double)T * E * 4,
+        b200q_moe_route_ex(y->rlog, T, E, K, 1, y->idx, y->wts, y->group_off, y->perm_tok, y->pair_pos, y->tile_tab,
+                           y->n_tiles, stream));
+    // every (token, choice) pair's input, scaled by its routing weight, in expert order
+    TRY(EW, 2.0 * P * W * es, b200q_scatter_scaled_rows(y->h2, y->pair_pos, y->wts, K, y->esrc, T, W, dt, stream));
+    TRY(B200Q_PROF_GEMM, 2.0 * P * 2.0 * F * W,
+        b200q_linear_grouped(y->esrc, W, nullptr, l.experts_gate_up, 2LL * F * W, y->egu, 2 * F, y->group_off, E, P,
+                             2 * F, W, dt, y->tile_tab, y->n_tiles, stream));
+    TRY(EW, 3.0 * P * F * es, b200q_silu_glu(y->egu, y->eact, P, F, dt, stream));
+    TRY(B200Q_PROF_GEMM, 2.0 * P * (double)F * W,
+        b200q_linear_grouped(y->eact, F, nullptr, l.experts_down, (long long)W * F, y->eout, W, y->group_off, E, P, W, F,
+                             dt, y->tile_tab, y->n_tiles, stream));
+    return B200Q_OK;
+  };
+
+  for (int li = 0; li < c.n_layers; ++li) {
+    const b200q_layered_layer& l = y->layers[li];
+    const b200q_layer_desc& d = l.d;
+    const bool has_ff = d.ff != B200Q_FF_NONE;
+    if (post) {
+      // x <- norm1(alpha x + ls1 * mixer(x + conv1 x));  x <- norm2(alpha x + ls2 * ff(x + conv2 x))
+      for (int sub = 0; sub < (has_ff ? 2 : 1); ++sub) {
+        void* hin = sub ? y->h2 : y->h1;
+        if (c.input_taps > 0)
+          TRY(EW, (double)T * W * (4 + es),
+              b200q_causal_conv(y->x, W, 1, sub ? l.canon2 : l.canon1, nullptr, W, c.input_taps, 0, 1,
+                                y->state + (sub ? l.canon2_off : l.canon1_off), y->state_slot_floats, b->seq_desc,
+                                b->row_seq, b->n_rows, hin, W, 0, T, dt, stream));
+        else if (dt == B200Q_DTYPE_F32)
+          TRY(EW, 8.0 * T * W, b200q_copy_f32(y->x, (float*)hin, (int64_t)T * W, stream));
+        else
+          TRY(EW, 6.0 * T * W, b200q_f32_to_bf16(y->x, hin, (int64_t)T * W, stream));
+        if (sub == 0) {
+          if ((rc = run_mixer(l))) return rc;
+          TRY(EW, (double)T * W * (8 + es),
+              b200q_group_rmsnorm(y->x, nullptr, y->mix, nullptr, 0, l.ls1, c.residual_alpha, l.norm1, groups, c.rms_eps,
+                                  y->x, nullptr, T, W, dt, stream));
+        } else {
+          B200Q_CHECK_ARG(d.ff == B200Q_FF_MOE_SIGMOID, "layer %d: feed-forward %d is not built for the post-norm form",
+                          li, d.ff);
+          if ((rc = run_moe_sigmoid(l))) return rc;
+          TRY(EW, (double)T * W * (8 + d.top_k * es),
+              b200q_group_rmsnorm(y->x, nullptr, y->eout, y->pair_pos, d.top_k, l.ls2, c.residual_alpha, l.norm2, groups,
+                                  c.rms_eps, y->x, nullptr, T, W, dt, stream));
+        }
+      }
+      if (y->tap) TRY(EW, 8.0 * T * W, b200q_copy_f32(y->x, y->tap + (int64_t)li * T * W, (int64_t)T * W, stream));
+      continue;
+    }
+    TRY(EW, (double)T * W * (4 + 2 * es),
+        b200q_centered_rmsnorm(y->x, nullptr, l.norm1, l.norm2, y->h1, has_ff ? y->h2 : nullptr, T, W, c.rms_eps, dt,
+                               stream));
+    if ((rc = run_mixer(l))) return rc;
     // ---- feed-forward and the layer's sum ----
     if (d.ff == B200Q_FF_POLYNORM) {
       LIN(y->h2, W, l.up, nullptr, y->ffh, d.ff_dim, d.ff_dim, W, 0);
@@ -441,9 +677,14 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
   }
   if (b->n_sample > 0) {
     const int n = b->n_sample;
-    TRY(EW, (double)n * W * (4 + es),
-        b200q_centered_rmsnorm(y->x, b->sample_rows, (const float*)m->final_norm, nullptr, y->sel, nullptr, n, W,
-                               c.rms_eps, dt, stream));
+    if (post)
+      TRY(EW, (double)n * W * (4 + es),
+          b200q_group_rmsnorm(y->x, b->sample_rows, nullptr, nullptr, 0, nullptr, 1.f, (const float*)m->final_norm, groups,
+                              c.rms_eps, nullptr, y->sel, n, W, dt, stream));
+    else
+      TRY(EW, (double)n * W * (4 + es),
+          b200q_centered_rmsnorm(y->x, b->sample_rows, (const float*)m->final_norm, nullptr, y->sel, nullptr, n, W,
+                                 c.rms_eps, dt, stream));
     TRY(B200Q_PROF_GEMM, 2.0 * n * (double)c.vocab * W,
         b200q_linear(y->sel, W, m->lm_head, nullptr, y->logits, c.vocab, n, c.vocab, W, dt, 1, stream));
     if (!b->no_sampling) {

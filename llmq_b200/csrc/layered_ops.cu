@@ -1,4 +1,4 @@
-// layered_ops.cu — kernels of the layered architectures (B200Q_ARCH_RAMOPEL): fp32 residual stream,
+// layered_ops.cu — kernels of the layered architectures (parallel pre-norm form): fp32 residual stream,
 // zero-centred RMS norms, a shape-agnostic linear layer (plain / per-head batched / grouped by expert),
 // latent attention over a paged latent cache with a sliding window, the generalized delta-rule
 // recurrence over fp32 state slots, PolyNorm, clamped gated experts with top-k routing.
@@ -10,35 +10,9 @@
 // per row, so a token's result is the same alone, in a chunk or in a mixed batch.
 #include <stdlib.h>
 
-#include "common.cuh"
+#include "layered_common.cuh"
 
 namespace b200q {
-
-template <typename T> __device__ __forceinline__ float ldf(const T* p);
-template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
-template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
-template <typename T> __device__ __forceinline__ void stf(T* p, float v);
-template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
-template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
-
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-// sum over the block (blockDim.x a multiple of 32, <= 1024); red: >= 32 floats of shared memory.
-// Every thread adds the warp partials in the same order, so all threads hold the same bits.
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  __syncthreads();
-  if (lane == 0) red[w] = v;
-  __syncthreads();
-  float t = 0.f;
-  for (int i = 0; i < nw; ++i) t += red[i];
-  return t;
-}
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 
 // ------------------------------------------------------------------------------------------------
 // embedding into the fp32 residual: x[t,:] = table[id,:] * scale (ids < 0: see resolve in elementwise.cu)
@@ -1107,7 +1081,8 @@ __global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ 
 // weights = softmax over the chosen logits.  k <= 32.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int Tn, int E, int top,
-                                                        int32_t* __restrict__ idx, float* __restrict__ wts) {
+                                                        int score_mode, int32_t* __restrict__ idx,
+                                                        float* __restrict__ wts) {
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= Tn) return;
   const float* z = logits + (long long)t * E;
@@ -1148,7 +1123,8 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   const float sum = warp_sum(ex);
   if (lane < top) {
     idx[(long long)t * top + lane] = chosen_i;
-    wts[(long long)t * top + lane] = ex / sum;
+    // score_mode 1: every chosen expert keeps its own sigmoid score (the order by logit is the order by score)
+    wts[(long long)t * top + lane] = score_mode == 1 ? sigmoidf_(chosen_v) : ex / sum;
   }
 }
 
@@ -1266,26 +1242,9 @@ __global__ void __launch_bounds__(256) copy_f32_kernel(const float* __restrict__
     out[e] = in[e];
 }
 
-static inline int grid_for(long long total, int block = 256) {
-  long long g = (total + block - 1) / block;
-  return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
-}
-static inline bool is_dtype(int d) { return d == B200Q_DTYPE_BF16 || d == B200Q_DTYPE_F32; }
-
 }  // namespace b200q
 
 using namespace b200q;
-
-#define DISPATCH_T(dtype, ...)                   \
-  do {                                           \
-    if ((dtype) == B200Q_DTYPE_F32) {            \
-      using T = float;                           \
-      __VA_ARGS__;                               \
-    } else {                                     \
-      using T = bf16;                            \
-      __VA_ARGS__;                               \
-    }                                            \
-  } while (0)
 
 extern "C" {
 
@@ -1587,12 +1546,19 @@ int b200q_clamped_glu(const void* gate_up, void* y, int64_t rows, int F, float l
 
 int b200q_moe_route(const float* logits, int T_, int E, int top, int32_t* idx, float* wts, int32_t* group_off,
                     int32_t* perm_tok, int32_t* pair_pos, int32_t* tile_tab, int32_t* n_tiles, void* stream) {
+  return b200q_moe_route_ex(logits, T_, E, top, 0, idx, wts, group_off, perm_tok, pair_pos, tile_tab, n_tiles, stream);
+}
+
+int b200q_moe_route_ex(const float* logits, int T_, int E, int top, int score_mode, int32_t* idx, float* wts,
+                       int32_t* group_off, int32_t* perm_tok, int32_t* pair_pos, int32_t* tile_tab, int32_t* n_tiles,
+                       void* stream) {
+  B200Q_CHECK_ARG(score_mode == 0 || score_mode == 1, "moe_route: score_mode=%d unknown", score_mode);
   B200Q_CHECK_ARG(!tile_tab == !n_tiles, "moe_route: tile_tab and n_tiles go together");
   B200Q_CHECK_ARG(logits && idx && wts && group_off && perm_tok && pair_pos && T_ >= 0 && E > 0 && top > 0 &&
                       top <= 32 && top <= E && E <= 4096,
                   "moe_route: bad argument (E=%d top=%d)", E, top);
   if (T_ == 0) return B200Q_OK;
-  moe_route_kernel<<<(T_ + 3) / 4, 128, 0, as_stream(stream)>>>(logits, T_, E, top, idx, wts);
+  moe_route_kernel<<<(T_ + 3) / 4, 128, 0, as_stream(stream)>>>(logits, T_, E, top, score_mode, idx, wts);
   B200Q_LAUNCH_CHECK();
   moe_plan_kernel<<<1, 1024, (size_t)(3 * E + 1) * sizeof(int32_t), as_stream(stream)>>>(idx, T_ * top, top, E,
                                                                                           group_off, perm_tok, pair_pos,

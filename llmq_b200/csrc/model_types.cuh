@@ -26,8 +26,17 @@ struct b200q_layered_layer {
   const float* router_bias = nullptr;
   const void *experts_gate_up = nullptr, *experts_down = nullptr, *shared_gate_up = nullptr,
              *shared_down = nullptr, *shared_gate = nullptr;
+  // post-norm form: layer scales and input convolutions of the two sublayers
+  const float *ls1 = nullptr, *ls2 = nullptr, *canon1 = nullptr, *canon2 = nullptr;
+  // gated delta (proj = [q | k | v | gate] rows), chunk attention (proj = [q | k | gate] rows; q_norm / kv_norm
+  // are the per-head norms of queries and keys), selective scan (proj = [x | z] rows)
+  const void* ba = nullptr;  // gated delta: [beta | decay input] rows
+  const float *conv_w = nullptr, *conv_b = nullptr, *a_log = nullptr, *dt_bias = nullptr, *r1 = nullptr, *r2 = nullptr;
+  const void *x_proj = nullptr, *dt_proj = nullptr;
+  const float *dt_b = nullptr, *dvec = nullptr;
   int64_t cache_block_off = 0;  // bytes per block of the cache regions before this layer's (own cache only)
-  int64_t state_off = 0;        // floats into a state slot
+  int64_t state_off = 0;        // floats into a state slot: the recurrent state
+  int64_t conv_off = 0, canon1_off = 0, canon2_off = 0;  // ... the carried inputs of the convolutions
   double* freq = nullptr;       // device, [rot_dims/2]
 };
 
@@ -38,6 +47,10 @@ struct b200q_layered {
   float* state = nullptr;
   int64_t n_slots = 0;
   float* tap = nullptr;
+  const void* pos = nullptr;  // learned position table [pos_rows, W]
+  int64_t pos_rows = 0;
+  float *cvf = nullptr, *baf = nullptr, *dtr = nullptr;  // fp32: convolved q|k|v (+ raw outputs), beta|g, step sizes
+  void *xc = nullptr, *xp = nullptr;                     // selective scan: convolved x, [dt | B | C] rows
   // workspace views (element type = cfg.dtype unless float)
   float *dscr = nullptr;  // delta rule: per-token vectors and raw outputs of a step (fp32)
   float *x = nullptr, *qa = nullptr, *rlog = nullptr, *wts = nullptr, *sgate = nullptr, *logits = nullptr;

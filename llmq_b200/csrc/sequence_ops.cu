@@ -1,0 +1,676 @@
+// sequence_ops.cu — kernels of the post-norm layered form and of the mixers that carry per-sequence state
+// besides a paged cache: grouped RMS norm over the scaled residual sum, per-channel causal convolutions
+// continued from the inputs a sequence left in its state slot, the gated delta rule, chunked grouped-query
+// attention over a cache of raw keys that double as values (sink softmax, soft cap, logarithmic distance
+// penalty), the selective scan, and the pieces of a sigmoid-routed mixture whose weight scales the expert's
+// input.
+//
+// As in layered_ops.cu every kernel is a template over the element type of matrices, activations and cache
+// (bf16 or fp32), and what has to be exact is fp32 in both: the residual sum and its norms, scores and
+// softmax weights, unit norms, decays, step sizes, gates of the recurrences and the recurrent states.
+// Every reduction has a fixed order per row and every loop over keys or tokens starts at a place that
+// depends only on the token's position in its sequence (chunk start, sequence start), so a token's result
+// does not depend on how its prompt was cut into steps, on its batch-mates, or on pages and slots.
+#include "layered_common.cuh"
+
+namespace b200q {
+
+// seq_desc[4*s + ...] = {first batch row, tokens this step, position of the first of them, state slot}
+struct SeqView {
+  int row0, n, pos0, slot;
+};
+__device__ __forceinline__ SeqView seq_view(const int32_t* __restrict__ seq_desc, int s) {
+  const int4 v = *reinterpret_cast<const int4*>(seq_desc + 4 * s);
+  return {v.x, v.y, v.z, v.w};
+}
+
+// ------------------------------------------------------------------------------------------------
+// embedding + learned position vector into the fp32 residual
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) embed_pos_kernel(const int32_t* __restrict__ ids,
+                                                        const int32_t* __restrict__ prev_out,
+                                                        const T* __restrict__ table, const T* __restrict__ pos_table,
+                                                        const int32_t* __restrict__ positions,
+                                                        float* __restrict__ out, int Tn, int W) {
+  const long long total = (long long)Tn * W;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / W), c = (int)(i % W);
+    int id = __ldg(ids + t);
+    if (id < 0) id = prev_out[-1 - id];
+    float v = ldf(table + (long long)id * W + c);
+    if (pos_table) v += ldf(pos_table + (long long)positions[t] * W + c);
+    out[i] = v;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// grouped RMS norm of v = alpha * x + scale * add (one CTA per row; v is kept in shared memory between
+// the sums and the scaling, so x may be overwritten in place).  add: the row itself, or the sum of the
+// `top` rows pair_pos[r*top + k] (outputs of the routed experts, in ascending k).
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) group_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
+                                                         const T* __restrict__ add,
+                                                         const int32_t* __restrict__ pair_pos, int top,
+                                                         const float* __restrict__ scale, float alpha,
+                                                         const float* __restrict__ w, int groups, float eps,
+                                                         float* yf, T* __restrict__ yt, int W) {
+  extern __shared__ float sm[];
+  float* v = sm;        // [W]
+  float* inv = sm + W;  // [groups]
+  const int r = blockIdx.x;
+  const long long src = rows ? rows[r] : r;
+  const float* xr = x + src * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float a = 0.f;
+    if (add) {
+      if (pair_pos) {
+        for (int k = 0; k < top; ++k) a += ldf(add + (long long)pair_pos[src * top + k] * W + c);
+      } else {
+        a = ldf(add + src * W + c);
+      }
+      if (scale) a *= scale[c];
+    }
+    v[c] = fmaf(alpha, xr[c], a);
+  }
+  __syncthreads();
+  const int gs = W / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int g = warp; g < groups; g += nw) {
+    float ss = 0.f;
+    for (int c = lane; c < gs; c += 32) ss = fmaf(v[g * gs + c], v[g * gs + c], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) inv[g] = 1.f / sqrtf(ss / (float)gs + eps);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float y = v[c] * inv[c / gs] * w[c];
+    if (yf) yf[(long long)r * W + c] = y;
+    if (yt) stf(yt + (long long)r * W + c, y);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// per-channel causal convolution over time, continued across steps.  A sequence's state region holds the
+// last taps-1 inputs of the channel, oldest first: entry e is the input at position pos0 - (taps-1) + e.
+// Inputs before position 0 are zeros, whatever the slot holds.  One thread per (token, channel).
+// ------------------------------------------------------------------------------------------------
+constexpr int CONV_MAX_TAPS = 16;
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) causal_conv_kernel(const TI* __restrict__ in, int ld_in,
+                                                          const float* __restrict__ w,
+                                                          const float* __restrict__ bias, int C, int taps, int act,
+                                                          int add_input, const float* __restrict__ state,
+                                                          long long slot_stride, const int32_t* __restrict__ seq_desc,
+                                                          const int32_t* __restrict__ row_seq, TO* __restrict__ out,
+                                                          int ld_out) {
+  const int t = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
+  if (c >= C) return;
+  const SeqView s = seq_view(seq_desc, row_seq[t]);
+  const int tt = t - s.row0;
+  const float* st = state + (long long)s.slot * slot_stride;
+  float acc = bias ? bias[c] : 0.f, cur = 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int idx = tt - (taps - 1) + j;  // source token, relative to the first token of this portion
+    float xv = 0.f;
+    if (idx >= 0) xv = ldf(in + (long long)(s.row0 + idx) * ld_in + c);
+    else if (s.pos0 + idx >= 0) xv = st[(long long)(taps - 1 + idx) * C + c];
+    acc = fmaf(w[(long long)c * taps + j], xv, acc);
+    cur = xv;
+  }
+  if (act == 1) acc = siluf_(acc);
+  if (add_input) acc += cur;
+  stf(out + (long long)t * ld_out + c, acc);
+}
+
+// the state after the portion: the last taps-1 inputs, taken from the portion and, where it is shorter,
+// from the old state (read completely before anything is written)
+template <typename TI>
+__global__ void __launch_bounds__(256) conv_state_kernel(const TI* __restrict__ in, int ld_in, int C, int taps,
+                                                         float* __restrict__ state, long long slot_stride,
+                                                         const int32_t* __restrict__ seq_desc) {
+  const int c = blockIdx.y * 256 + threadIdx.x;
+  if (c >= C) return;
+  const SeqView s = seq_view(seq_desc, blockIdx.x);
+  float* st = state + (long long)s.slot * slot_stride;
+  float keep[CONV_MAX_TAPS];
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+    if (i < taps - 1) {
+      const int idx = s.n - (taps - 1) + i;
+      float xv = 0.f;
+      if (idx >= 0) xv = ldf(in + (long long)(s.row0 + idx) * ld_in + c);
+      else if (s.pos0 + idx >= 0) xv = st[(long long)(taps - 1 + idx) * C + c];
+      keep[i] = xv;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i)
+    if (i < taps - 1) st[(long long)i * C + c] = keep[i];
+}
+
+// ------------------------------------------------------------------------------------------------
+// gated delta rule, three launches.
+//   prepare (CTA per token): q, k -> unit vectors per head (q also times dim^-1/2), in place in the fp32
+//           qkv rows; ba row (beta logits | decay inputs) -> (beta | g) in place
+//   recur   (CTA per sequence x head, thread j = value column j, the state column S[0..dim) in registers):
+//           S <- g S;  u = beta (v_j - k.S);  S <- S + k u;  o_j = q.S   -> raw [T, heads*vdim] (fp32)
+//           k, q, beta, g of 8 tokens at a time are staged in shared memory
+//   finish  (CTA per token x head): out = raw / rms(raw) * out_norm * silu(gate)
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) gdelta_prepare_kernel(float* __restrict__ qkv, float* __restrict__ ba,
+                                                             const float* __restrict__ a_log,
+                                                             const float* __restrict__ dt_bias, int heads,
+                                                             int kv_heads, int dim, int vdim) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ldq = 2 * kv_heads * dim + heads * vdim;
+  float* row = qkv + (long long)t * ldq;
+  const float qs = 1.f / sqrtf((float)dim);
+  for (int vh = warp; vh < 2 * kv_heads; vh += 4) {  // vectors 0..G-1: q heads, G..2G-1: k heads
+    float* p = row + (long long)vh * dim;
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) ss = fmaf(p[d], p[d], ss);
+    ss = warp_sum(ss);
+    const float inv = (vh < kv_heads ? qs : 1.f) / sqrtf(ss + 1e-6f);
+    for (int d = lane; d < dim; d += 32) p[d] *= inv;
+  }
+  float* b = ba + (long long)t * 2 * heads;
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    const float beta = sigmoidf_(b[h]);
+    const float g = expf(-expf(a_log[h]) * softplusf_(b[heads + h] + dt_bias[h]));
+    b[h] = beta;
+    b[heads + h] = g;
+  }
+}
+
+constexpr int GDELTA_G = 8;  // tokens staged per barrier pair
+template <int DT>
+__global__ void gdelta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ bg,
+                                    float* __restrict__ state, long long slot_stride,
+                                    const int32_t* __restrict__ seq_desc, int heads, int kv_heads, int dim, int vdim,
+                                    float* __restrict__ raw) {
+  extern __shared__ float sm[];
+  float* kq = sm;                           // [G][2*dim]: k then q of the token
+  float* bgs = sm + GDELTA_G * 2 * dim;     // [G][2]
+  const SeqView s = seq_view(seq_desc, blockIdx.x);
+  const int h = blockIdx.y, j = threadIdx.x, kvh = h / (heads / kv_heads);
+  const int GD = kv_heads * dim, ldq = 2 * GD + heads * vdim, HV = heads * vdim;
+  const bool on = j < vdim;
+  float* st = state + (long long)s.slot * slot_stride + (long long)h * dim * vdim;
+  float S[DT];
+#pragma unroll
+  for (int q = 0; q < DT; ++q) S[q] = (on && q < dim && s.pos0 > 0) ? st[(long long)q * vdim + j] : 0.f;
+  for (int g0 = 0; g0 < s.n; g0 += GDELTA_G) {
+    const int cnt = min(GDELTA_G, s.n - g0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < cnt * 2 * dim; e += blockDim.x) {
+      const int tk = e / (2 * dim), i = e % (2 * dim);
+      const float* r = qkv + (long long)(s.row0 + g0 + tk) * ldq;
+      kq[e] = i < dim ? r[GD + kvh * dim + i] : r[kvh * dim + i - dim];
+    }
+    for (int e = threadIdx.x; e < cnt * 2; e += blockDim.x) {
+      const int tk = e >> 1;
+      bgs[e] = bg[(long long)(s.row0 + g0 + tk) * 2 * heads + (e & 1) * heads + h];
+    }
+    __syncthreads();
+    if (!on) continue;
+    for (int tk = 0; tk < cnt; ++tk) {
+      const long long r = s.row0 + g0 + tk;
+      const float* kk = kq + tk * 2 * dim;
+      const float* qq = kk + dim;
+      const float beta = bgs[2 * tk], g = bgs[2 * tk + 1], vj = qkv[r * ldq + 2 * GD + h * vdim + j];
+      float kS = 0.f;
+#pragma unroll
+      for (int q = 0; q < DT; ++q)
+        if (q < dim) {
+          S[q] *= g;
+          kS = fmaf(kk[q], S[q], kS);
+        }
+      const float u = beta * (vj - kS);
+      float o = 0.f;
+#pragma unroll
+      for (int q = 0; q < DT; ++q)
+        if (q < dim) {
+          S[q] = fmaf(kk[q], u, S[q]);
+          o = fmaf(S[q], qq[q], o);
+        }
+      raw[r * HV + h * vdim + j] = o;
+    }
+  }
+  if (on) {
+#pragma unroll
+    for (int q = 0; q < DT; ++q)
+      if (q < dim) st[(long long)q * vdim + j] = S[q];
+  }
+}
+
+template <typename T>
+__global__ void gdelta_finish_kernel(const float* __restrict__ raw, const T* __restrict__ gate, int ld_gate,
+                                     const float* __restrict__ out_norm, int heads, int vdim, float eps,
+                                     T* __restrict__ out) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+  const bool on = j < vdim;
+  const long long at = (long long)t * heads * vdim + h * vdim + j;
+  const float o = on ? raw[at] : 0.f;
+  const float sso = block_sum(o * o, red);
+  if (on) {
+    const float gv = siluf_(ldf(gate + (long long)t * ld_gate + h * vdim + j));
+    stf(out + at, o / sqrtf(sso / (float)vdim + eps) * out_norm[j] * gv);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// chunk attention, step 1 (CTA per token): per-head RMS norm of the queries with BOTH norm weights folded
+// in (q / rms(q) * w_q * w_k: the key norm's weight moves to the query side, its 1/rms is applied to the
+// score), and the raw keys into the paged cache row of the token.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) chunk_attn_prep_kernel(const T* __restrict__ proj, int ldp, int heads,
+                                                              int kv_heads, int dim, const float* __restrict__ w_qn,
+                                                              const float* __restrict__ w_kn,
+                                                              const int32_t* __restrict__ slot_mapping,
+                                                              float* __restrict__ qs, T* __restrict__ cache, float eps) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* pr = proj + (long long)t * ldp;
+  for (int h = warp; h < heads; h += 4) {
+    const T* q = pr + (long long)h * dim;
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) {
+      const float v = ldf(q + d);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)dim + eps);
+    float* o = qs + ((long long)t * heads + h) * dim;
+    for (int d = lane; d < dim; d += 32) o[d] = ldf(q + d) * inv * w_qn[d] * w_kn[d];
+  }
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  const int GD = kv_heads * dim;
+  const T* k = pr + (long long)heads * dim;
+  T* row = cache + (long long)slot * GD;
+  for (int e = threadIdx.x; e < GD; e += blockDim.x) row[e] = k[e];
+}
+
+// step 2: one CTA per (token, key/value head, group of 8 query heads that share it).  Tiles of 32 cached
+// keys are staged in shared memory once and used by up to 8 query heads (warp = head; lane = key for the
+// scores, lane = output dims for the weighted sum).  The sink enters as the initial state of the online
+// softmax: running maximum 0, denominator 1, no value.  Tiles start at the first key of the token's chunk.
+template <typename T, int ACC>
+__global__ void __launch_bounds__(256) chunk_attn_kernel(const float* __restrict__ qs, const T* __restrict__ cache,
+                                                         const int32_t* __restrict__ block_table, int bt_stride,
+                                                         const int32_t* __restrict__ row_seq,
+                                                         const int32_t* __restrict__ positions, int heads,
+                                                         int kv_heads, int dim, int block_size, int chunk, float scale,
+                                                         float softcap, const float* __restrict__ r1,
+                                                         const float* __restrict__ r2, const T* __restrict__ gate,
+                                                         int ld_gate, float eps, T* __restrict__ out) {
+  extern __shared__ float sm[];
+  const int KS = dim + 1;
+  float* qsm = sm;              // [8][dim]
+  float* ksm = sm + 8 * dim;    // [32][dim+1]
+  float* kinv = ksm + 32 * KS;  // [32]
+  const int t = blockIdx.x, g = blockIdx.y, rep = heads / kv_heads;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hg = blockIdx.z * 8 + warp;  // head within the group
+  const bool live = hg < rep;
+  const int h = g * rep + hg;
+  const int p = positions[t];
+  const int32_t* bt = block_table + (long long)row_seq[t] * bt_stride;
+  const int lo = chunk > 0 ? p - p % chunk : 0;
+  const int GD = kv_heads * dim;
+  for (int e = threadIdx.x; e < 8 * dim; e += blockDim.x) {
+    const int hh = blockIdx.z * 8 + e / dim;
+    qsm[e] = hh < rep ? qs[((long long)t * heads + g * rep + hh) * dim + e % dim] : 0.f;
+  }
+  const float c1 = live ? r1[h] : 0.f, c2 = live ? r2[h] : 0.f;
+  float m = 0.f, l = 1.f;  // the sink: a score of zero without a value
+  float acc[ACC];
+#pragma unroll
+  for (int i = 0; i < ACC; ++i) acc[i] = 0.f;
+  const float* qh = qsm + warp * dim;
+  for (int j0 = lo; j0 <= p; j0 += 32) {
+    const int n = min(32, p + 1 - j0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
+      const int j = e / dim, d = e % dim, pos = j0 + j;
+      const long long row = (long long)bt[pos / block_size] * block_size + pos % block_size;
+      ksm[j * KS + d] = ldf(cache + row * GD + (long long)g * dim + d);
+    }
+    __syncthreads();
+    for (int j = warp; j < n; j += 8) {
+      float ss = 0.f;
+      for (int d = lane; d < dim; d += 32) ss = fmaf(ksm[j * KS + d], ksm[j * KS + d], ss);
+      ss = warp_sum(ss);
+      if (lane == 0) kinv[j] = 1.f / sqrtf(ss / (float)dim + eps);
+    }
+    __syncthreads();
+    if (!live) continue;
+    float s = -INFINITY;
+    if (lane < n) {
+      const float* kr = ksm + lane * KS;
+      float dot = 0.f;
+      for (int d = 0; d < dim; ++d) dot = fmaf(qh[d], kr[d], dot);
+      s = dot * kinv[lane] * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      s -= c1 * log1pf(c2 * (float)(p - (j0 + lane)));
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);
+    const float pl = lane < n ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(pl);
+#pragma unroll
+    for (int i = 0; i < ACC; ++i) acc[i] *= corr;
+    for (int j = 0; j < n; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, pl, j);
+      const float* kr = ksm + j * KS;
+#pragma unroll
+      for (int i = 0; i < ACC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < dim) acc[i] = fmaf(pj, kr[d], acc[i]);
+      }
+    }
+    m = m_new;
+  }
+  if (!live) return;
+  const float inv = 1.f / l;
+  const T* gr = gate + (long long)t * ld_gate + (long long)h * dim;
+  T* o = out + ((long long)t * heads + h) * dim;
+#pragma unroll
+  for (int i = 0; i < ACC; ++i) {
+    const int d = lane + 32 * i;
+    if (d < dim) stf(o + d, acc[i] * inv * sigmoidf_(ldf(gr + d)));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// selective scan: one CTA per (sequence, 128 channels), thread = channel, the channel's state S[0..N) and
+// its decay rates A[n] = -exp(a_log) in registers; B and C of 8 tokens at a time are staged in shared
+// memory (they are shared by all channels).  State layout in the slot: [N][inner] (coalesced over channels).
+// ------------------------------------------------------------------------------------------------
+constexpr int SCAN_G = 8;
+template <typename T, int NT>
+__global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict__ x, const float* __restrict__ dt_raw,
+                                                             const T* __restrict__ bc, int ld_bc, int b_off,
+                                                             const T* __restrict__ z, int ld_z,
+                                                             const float* __restrict__ a_log,
+                                                             const float* __restrict__ dvec, float* __restrict__ state,
+                                                             long long slot_stride,
+                                                             const int32_t* __restrict__ seq_desc, int inner, int N,
+                                                             T* __restrict__ out) {
+  extern __shared__ float sm[];  // [G][2N]
+  const SeqView s = seq_view(seq_desc, blockIdx.x);
+  const int c = blockIdx.y * 128 + threadIdx.x;
+  const bool on = c < inner;
+  float* st = state + (long long)s.slot * slot_stride;
+  float S[NT], A[NT];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    const bool in = on && n < N;
+    S[n] = (in && s.pos0 > 0) ? st[(long long)n * inner + c] : 0.f;
+    A[n] = in ? -expf(a_log[(long long)c * N + n]) : 0.f;
+  }
+  const float dc = on ? dvec[c] : 0.f;
+  for (int g0 = 0; g0 < s.n; g0 += SCAN_G) {
+    const int cnt = min(SCAN_G, s.n - g0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < cnt * 2 * N; e += blockDim.x) {
+      const int tk = e / (2 * N), i = e % (2 * N);
+      sm[e] = ldf(bc + (long long)(s.row0 + g0 + tk) * ld_bc + b_off + i);
+    }
+    __syncthreads();
+    if (!on) continue;
+    for (int tk = 0; tk < cnt; ++tk) {
+      const long long r = s.row0 + g0 + tk;
+      const float* Bv = sm + tk * 2 * N;
+      const float* Cv = Bv + N;
+      const float dt = softplusf_(dt_raw[r * inner + c]), xv = ldf(x + r * inner + c), dx = dt * xv;
+      float y = 0.f;
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+        if (n < N) {
+          S[n] = fmaf(expf(dt * A[n]), S[n], dx * Bv[n]);
+          y = fmaf(S[n], Cv[n], y);
+        }
+      y = fmaf(dc, xv, y);
+      stf(out + r * inner + c, y * siluf_(ldf(z + r * ld_z + c)));
+    }
+  }
+  if (on) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+      if (n < N) st[(long long)n * inner + c] = S[n];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// pieces of a mixture whose routing weight scales the expert's input
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) scatter_scaled_rows_kernel(const T* __restrict__ src,
+                                                                  const int32_t* __restrict__ pair_pos,
+                                                                  const float* __restrict__ wts, int top,
+                                                                  T* __restrict__ dst, long long pairs, int W) {
+  const long long total = pairs * W;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long long)gridDim.x * blockDim.x) {
+    const long long p = e / W;
+    const int c = (int)(e % W);
+    stf(dst + (long long)pair_pos[p] * W + c, ldf(src + (p / top) * W + c) * wts[p]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) silu_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows,
+                                                       int F) {
+  const long long total = rows * F;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long long)gridDim.x * blockDim.x) {
+    const long long r = e / F;
+    const int c = (int)(e % F);
+    stf(y + e, siluf_(ldf(gu + r * 2 * F + c)) * ldf(gu + r * 2 * F + F + c));
+  }
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_embed_pos_f32(const int32_t* ids, const int32_t* prev_out, const void* table, const void* pos_table,
+                        const int32_t* positions, float* out, int T_, int W, int dtype, void* stream) {
+  B200Q_CHECK_ARG(ids && table && out && T_ >= 0 && W > 0 && is_dtype(dtype) && (!pos_table || positions),
+                  "embed_pos_f32: bad argument");
+  if (T_ == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (embed_pos_kernel<T><<<grid_for((long long)T_ * W), 256, 0, as_stream(stream)>>>(
+                        ids, prev_out, (const T*)table, (const T*)pos_table, positions, out, T_, W)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_group_rmsnorm(const float* x, const int32_t* rows, const void* add, const int32_t* pair_pos, int top,
+                        const float* scale, float alpha, const float* w, int groups, float eps, float* y_f32,
+                        void* y_t, int n, int W, int dtype, void* stream) {
+  if (groups <= 0) groups = 1;
+  B200Q_CHECK_ARG(x && w && (y_f32 || y_t) && n >= 0 && W > 0 && is_dtype(dtype) && W % groups == 0 &&
+                      (!pair_pos || (add && top > 0)) && (!rows || !add),
+                  "group_rmsnorm: bad argument (W=%d groups=%d)", W, groups);
+  if (n == 0) return B200Q_OK;
+  const size_t smem = (size_t)(W + groups) * sizeof(float);
+  B200Q_CHECK_ARG(smem <= 200 * 1024, "group_rmsnorm: a row of %d does not fit shared memory", W);
+  DISPATCH_T(dtype, {
+    if (smem > 48 * 1024)
+      B200Q_CUDA(cudaFuncSetAttribute(group_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    group_norm_kernel<T><<<n, 256, smem, as_stream(stream)>>>(x, rows, (const T*)add, pair_pos, top, scale, alpha, w,
+                                                              groups, eps, y_f32, (T*)y_t, W);
+  });
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_causal_conv(const void* in, int ld_in, int in_f32, const float* w, const float* bias, int C, int taps,
+                      int act, int add_input, float* state, long long slot_stride, const int32_t* seq_desc,
+                      const int32_t* row_seq, int n_seqs, void* out, int ld_out, int out_f32, int T_, int dtype,
+                      void* stream) {
+  B200Q_CHECK_ARG(in && w && state && seq_desc && row_seq && out && C > 0 && taps >= 1 && taps <= CONV_MAX_TAPS &&
+                      ld_in >= C && ld_out >= C && n_seqs >= 0 && T_ >= 0 && is_dtype(dtype) && (act == 0 || act == 1),
+                  "causal_conv: bad argument (C=%d taps=%d, at most %d taps)", C, taps, CONV_MAX_TAPS);
+  if (T_ == 0 || n_seqs == 0) return B200Q_OK;
+  const bool fi = in_f32 || dtype == B200Q_DTYPE_F32, fo = out_f32 || dtype == B200Q_DTYPE_F32;
+  cudaStream_t st = as_stream(stream);
+  dim3 grid(T_, (C + 255) / 256), sgrid(n_seqs, (C + 255) / 256);
+#define CONV(TI, TO)                                                                                              \
+  do {                                                                                                            \
+    causal_conv_kernel<TI, TO><<<grid, 256, 0, st>>>((const TI*)in, ld_in, w, bias, C, taps, act, add_input, state, \
+                                                     slot_stride, seq_desc, row_seq, (TO*)out, ld_out);           \
+    B200Q_LAUNCH_CHECK();                                                                                         \
+    if (taps > 1) {                                                                                               \
+      conv_state_kernel<TI><<<sgrid, 256, 0, st>>>((const TI*)in, ld_in, C, taps, state, slot_stride, seq_desc);  \
+      B200Q_LAUNCH_CHECK();                                                                                       \
+    }                                                                                                             \
+  } while (0)
+  if (fi && fo) CONV(float, float);
+  else if (fi) CONV(float, bf16);
+  else if (fo) CONV(bf16, float);
+  else CONV(bf16, bf16);
+#undef CONV
+  return B200Q_OK;
+}
+
+int b200q_gated_delta(float* qkv, float* ba, float* raw, const void* gate, int ld_gate, const float* a_log,
+                      const float* dt_bias, const float* out_norm, float* state, long long slot_stride,
+                      const int32_t* seq_desc, int n_seqs, int heads, int kv_heads, int dim, int vdim, float eps,
+                      void* out, int T_, int dtype, void* stream) {
+  B200Q_CHECK_ARG(qkv && ba && raw && gate && a_log && dt_bias && out_norm && state && seq_desc && out && heads > 0 &&
+                      kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && dim <= 256 && vdim > 0 && vdim <= 1024 &&
+                      n_seqs >= 0 && T_ >= 0 && is_dtype(dtype),
+                  "gated_delta: bad argument (heads=%d kv_heads=%d dim=%d (<= 256) vdim=%d (<= 1024))", heads,
+                  kv_heads, dim, vdim);
+  if (n_seqs == 0 || T_ == 0) return B200Q_OK;
+  cudaStream_t st = as_stream(stream);
+  float* q = qkv;
+  float* b = ba;
+  gdelta_prepare_kernel<<<T_, 128, 0, st>>>(q, b, a_log, dt_bias, heads, kv_heads, dim, vdim);
+  B200Q_LAUNCH_CHECK();
+  const int threads = (vdim + 31) & ~31;
+  const size_t smem = (size_t)GDELTA_G * (2 * dim + 2) * sizeof(float);
+  dim3 grid(n_seqs, heads);
+#define RECUR(DT)                                                                                                  \
+  gdelta_recur_kernel<DT><<<grid, threads, smem, st>>>(q, b, state, slot_stride, seq_desc, heads, kv_heads, dim, \
+                                                       vdim, raw)
+  if (dim <= 32) RECUR(32);
+  else if (dim <= 64) RECUR(64);
+  else if (dim <= 128) RECUR(128);
+  else RECUR(256);
+#undef RECUR
+  B200Q_LAUNCH_CHECK();
+  dim3 fgrid(T_, heads);
+  DISPATCH_T(dtype, (gdelta_finish_kernel<T><<<fgrid, threads, 0, st>>>(raw, (const T*)gate, ld_gate, out_norm, heads,
+                                                                        vdim, eps, (T*)out)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_chunk_attn_prep(const void* proj, int ldp, int heads, int kv_heads, int dim, const float* w_qn,
+                          const float* w_kn, const int32_t* slot_mapping, float* qs, void* cache, int T_, float eps,
+                          int dtype, void* stream) {
+  B200Q_CHECK_ARG(proj && w_qn && w_kn && slot_mapping && qs && cache && heads > 0 && kv_heads > 0 && dim > 0 &&
+                      ldp >= (heads + kv_heads) * dim && T_ >= 0 && is_dtype(dtype),
+                  "chunk_attn_prep: bad argument");
+  if (T_ == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (chunk_attn_prep_kernel<T><<<T_, 128, 0, as_stream(stream)>>>(
+                        (const T*)proj, ldp, heads, kv_heads, dim, w_qn, w_kn, slot_mapping, qs, (T*)cache, eps)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_chunk_attn(const float* qs, const void* cache, const int32_t* block_table, int bt_stride,
+                     const int32_t* row_seq, const int32_t* positions, int T_, int heads, int kv_heads, int dim,
+                     int block_size, int chunk, float scale, float softcap, const float* r1, const float* r2,
+                     const void* gate, int ld_gate, float eps, void* out, int dtype, void* stream) {
+  B200Q_CHECK_ARG(qs && cache && block_table && row_seq && positions && r1 && r2 && gate && out && heads > 0 &&
+                      kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && dim <= 512 && block_size > 0 && chunk >= 0 &&
+                      T_ >= 0 && is_dtype(dtype),
+                  "chunk_attn: bad argument (heads=%d kv_heads=%d dim=%d (<= 512))", heads, kv_heads, dim);
+  if (T_ == 0) return B200Q_OK;
+  const int rep = heads / kv_heads;
+  dim3 grid(T_, kv_heads, (rep + 7) / 8);
+  const size_t smem = (size_t)(8 * dim + 32 * (dim + 1) + 32) * sizeof(float);
+#define ATTN(TT, ACC)                                                                                               \
+  do {                                                                                                              \
+    if (smem > 48 * 1024)                                                                                           \
+      B200Q_CUDA(cudaFuncSetAttribute(chunk_attn_kernel<TT, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                      (int)smem));                                                                  \
+    chunk_attn_kernel<TT, ACC><<<grid, 256, smem, as_stream(stream)>>>(                                             \
+        qs, (const TT*)cache, block_table, bt_stride, row_seq, positions, heads, kv_heads, dim, block_size, chunk, \
+        scale, softcap, r1, r2, (const TT*)gate, ld_gate, eps, (TT*)out);                                           \
+  } while (0)
+#define ATTN_BY_DIM(TT)                    \
+  do {                                     \
+    if (dim <= 64) ATTN(TT, 2);            \
+    else if (dim <= 128) ATTN(TT, 4);      \
+    else if (dim <= 256) ATTN(TT, 8);      \
+    else ATTN(TT, 16);                     \
+  } while (0)
+  if (dtype == B200Q_DTYPE_F32) ATTN_BY_DIM(float);
+  else ATTN_BY_DIM(bf16);
+#undef ATTN_BY_DIM
+#undef ATTN
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_selective_scan(const void* x, const float* dt_raw, const void* bc, int ld_bc, int b_off, const void* z,
+                         int ld_z, const float* a_log, const float* d, float* state, long long slot_stride,
+                         const int32_t* seq_desc, int n_seqs, int inner, int N, void* out, int dtype, void* stream) {
+  B200Q_CHECK_ARG(x && dt_raw && bc && z && a_log && d && state && seq_desc && out && inner > 0 && N > 0 && N <= 256 &&
+                      b_off >= 0 && ld_bc >= b_off + 2 * N && ld_z >= inner && n_seqs >= 0 && is_dtype(dtype),
+                  "selective_scan: bad argument (inner=%d state=%d (<= 256))", inner, N);
+  if (n_seqs == 0) return B200Q_OK;
+  dim3 grid(n_seqs, (inner + 127) / 128);
+  const size_t smem = (size_t)SCAN_G * 2 * N * sizeof(float);
+#define SCAN(TT, NT)                                                                                              \
+  selective_scan_kernel<TT, NT><<<grid, 128, smem, as_stream(stream)>>>(                                          \
+      (const TT*)x, dt_raw, (const TT*)bc, ld_bc, b_off, (const TT*)z, ld_z, a_log, d, state, slot_stride, seq_desc, \
+      inner, N, (TT*)out)
+#define SCAN_BY_N(TT)                 \
+  do {                                \
+    if (N <= 16) SCAN(TT, 16);        \
+    else if (N <= 32) SCAN(TT, 32);   \
+    else if (N <= 64) SCAN(TT, 64);   \
+    else if (N <= 128) SCAN(TT, 128); \
+    else SCAN(TT, 256);               \
+  } while (0)
+  if (dtype == B200Q_DTYPE_F32) SCAN_BY_N(float);
+  else SCAN_BY_N(bf16);
+#undef SCAN_BY_N
+#undef SCAN
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_scatter_scaled_rows(const void* src, const int32_t* pair_pos, const float* wts, int top, void* dst, int T_,
+                              int W, int dtype, void* stream) {
+  B200Q_CHECK_ARG(src && pair_pos && wts && dst && top > 0 && T_ >= 0 && W > 0 && is_dtype(dtype),
+                  "scatter_scaled_rows: bad argument");
+  if (T_ == 0) return B200Q_OK;
+  const long long pairs = (long long)T_ * top;
+  DISPATCH_T(dtype, (scatter_scaled_rows_kernel<T><<<grid_for(pairs * W), 256, 0, as_stream(stream)>>>(
+                        (const T*)src, pair_pos, wts, top, (T*)dst, pairs, W)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int b200q_silu_glu(const void* gate_up, void* y, int64_t rows, int F, int dtype, void* stream) {
+  B200Q_CHECK_ARG(gate_up && y && rows >= 0 && F > 0 && is_dtype(dtype), "silu_glu: bad argument");
+  if (rows == 0) return B200Q_OK;
+  DISPATCH_T(dtype, (silu_glu_kernel<T><<<grid_for(rows * F), 256, 0, as_stream(stream)>>>((const T*)gate_up, (T*)y,
+                                                                                         rows, F)));
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+}  // extern "C"

@@ -49,19 +49,32 @@ class ModelConfig(C.Structure):
         ("dtype", C.c_int32),
         ("max_logit_rows", C.c_int32),
         ("state_slots", C.c_int32),
+        # form of a layer (layered architectures)
+        ("layer_form", C.c_int32),
+        ("norm_groups", C.c_int32),
+        ("residual_alpha", C.c_float),
+        ("input_taps", C.c_int32),
+        ("learned_pos", C.c_int32),
     ]
 
 
 ARCH_LLAMA = 0
 ARCH_GEMMA2 = 1
 ARCH_RAMOPEL = 2
+ARCH_NORIDRA = 3
+FORM_PARALLEL = 0
+FORM_POSTNORM = 1
 DTYPE_BF16 = 0
 DTYPE_F32 = 1
 MIXER_LATENT_ATTN = 1
 MIXER_GENERAL_DELTA = 2
+MIXER_GATED_DELTA = 3
+MIXER_CHUNK_ATTN = 4
+MIXER_SELECTIVE_SCAN = 5
 FF_NONE = 0
 FF_POLYNORM = 1
 FF_MOE = 2
+FF_MOE_SIGMOID = 3
 
 
 class LayerDesc(C.Structure):
@@ -71,6 +84,8 @@ class LayerDesc(C.Structure):
         ("window", C.c_int32), ("rot_dims", C.c_int32), ("rot_base", C.c_double), ("attn_scale", C.c_float),
         ("decay_rank", C.c_int32), ("ff", C.c_int32), ("ff_dim", C.c_int32), ("n_experts", C.c_int32),
         ("top_k", C.c_int32), ("expert_limit", C.c_float), ("shared_dim", C.c_int32), ("shared_limit", C.c_float),
+        ("kv_heads", C.c_int32), ("conv_taps", C.c_int32), ("softcap", C.c_float), ("chunk", C.c_int32),
+        ("inner", C.c_int32), ("state_dim", C.c_int32), ("dt_rank", C.c_int32),
     ]
 
 
@@ -184,6 +199,18 @@ SIGNATURES = {
     "b200q_polynorm": (_i, [_vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200q_clamped_glu": (_i, [_vp, _vp, _i64, _i, _f, _i, _vp]),
     "b200q_moe_route": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_moe_route_ex": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200q_embed_pos_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200q_group_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _f, _vp, _i, _f, _vp, _vp, _i, _i, _i, _vp]),
+    "b200q_causal_conv": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp, _ll, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp]),
+    "b200q_gated_delta": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _i, _f, _vp, _i, _i,
+                               _vp]),
+    "b200q_chunk_attn_prep": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _f, _i, _vp]),
+    "b200q_chunk_attn": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp, _vp, _i, _f, _vp, _i,
+                              _vp]),
+    "b200q_selective_scan": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "b200q_scatter_scaled_rows": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "b200q_silu_glu": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
     "b200q_layer_sum": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp]),
     "b200q_argmax_f32": (_i, [_vp, _vp, _i, _i, _vp]),
     "b200q_f32_to_bf16": (_i, [_vp, _vp, _i64, _vp]),

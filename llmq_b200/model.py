@@ -17,7 +17,7 @@ from typing import Dict, Iterable, List, Optional, Tuple
 import torch
 
 from . import lib as L
-from . import ramopel
+from . import noridra, ramopel
 
 BLOCK_SIZE = 16
 
@@ -188,7 +188,10 @@ GEMMA_2_2B = ModelSpec(hidden=2304, n_layers=26, n_q_heads=8, n_kv_heads=4, head
                        bos_token_id=2, name="gemma-2-2b", arch="gemma2", query_pre_attn_scalar=256.0,
                        attn_softcap=50.0, final_softcap=30.0, sliding_window=4096)
 BUILTIN_SPECS = {"llama-3-8b": LLAMA_3_8B, "llama-3.2-1b": LLAMA_32_1B,
-                 "gemma-2-9b": GEMMA_2_9B, "gemma-2-2b": GEMMA_2_2B, **ramopel.BUILTIN_SPECS}
+                 "gemma-2-9b": GEMMA_2_9B, "gemma-2-2b": GEMMA_2_2B, **ramopel.BUILTIN_SPECS,
+                 **noridra.BUILTIN_SPECS}
+# config.json "architecture" -> the module that reads it (layered designs; HF-style configs carry "architectures")
+LAYERED_DESIGNS = {ramopel.ARCHITECTURE: ramopel.RamopelSpec, noridra.ARCHITECTURE: noridra.NoridraSpec}
 
 
 def rope_table(max_pos: int, head_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
@@ -298,24 +301,24 @@ def resolve_model(model_name: str) -> Tuple[ModelSpec, Optional[str]]:
     with open(cfg_path) as f:
         cfg = json.load(f)
     name = os.path.basename(os.path.normpath(model_name))
-    if cfg.get("architecture") == ramopel.ARCHITECTURE:
+    if cfg.get("architecture") in LAYERED_DESIGNS:
         ckpt = os.path.join(model_name, "model.safetensors")
         shapes = ramopel.checkpoint_shapes(ckpt) if os.path.exists(ckpt) else None
-        return ramopel.RamopelSpec.from_config(cfg, shapes, name=name), model_name
+        return LAYERED_DESIGNS[cfg["architecture"]].from_config(cfg, shapes, name=name), model_name
     return ModelSpec.from_hf_config(cfg, name=name), model_name
 
 
 def checkpoint_engine_weights(spec, model_dir: str) -> Iterable[Tuple[str, torch.Tensor]]:
     """the engine-layout weights of the checkpoint in `model_dir`, for whatever architecture `spec` is"""
     if getattr(spec, "layered", False):
-        return ramopel.engine_weights(spec, ramopel.load_checkpoint(os.path.join(model_dir, "model.safetensors")))
+        return spec.engine_weights(ramopel.load_checkpoint(os.path.join(model_dir, "model.safetensors")))
     return fuse_hf_weights(spec, load_hf_state_dict(model_dir))
 
 
 def random_weights(spec, seed: int, device) -> Iterable[Tuple[str, torch.Tensor]]:
     """random-init engine-layout weights for whatever architecture `spec` is (benchmarks)"""
     if getattr(spec, "layered", False):
-        return ramopel.engine_weights(spec, ramopel.random_checkpoint(spec, seed, device))
+        return spec.engine_weights(spec.random_checkpoint(seed, device))
     return random_engine_weights(spec, seed, device)
 
 
@@ -391,8 +394,9 @@ class NativeModel:
         torch.cuda.synchronize(self.device)
 
     def _init_layered(self, weights, max_tokens, max_seqs, num_blocks, gpu_memory_utilization, max_logit_rows):
-        """a layered architecture (Ramopel): one b200q_layer_desc per layer, a paged cache of latents for the
-        attention layers that own one, and one fp32 recurrent-state slot per live sequence"""
+        """a layered architecture (Ramopel, Noridra): one b200q_layer_desc per layer, a paged cache for the
+        attention layers that own one, and one fp32 state slot per live sequence (recurrent states and the
+        carried inputs of convolutions)"""
         spec, lib = self.spec, self.lib
         if self.dtype not in (torch.bfloat16, torch.float32):
             raise ValueError(f"dtype {self.dtype} unsupported: bfloat16 or float32")
@@ -400,8 +404,8 @@ class NativeModel:
         self.cfg = L.ModelConfig(
             hidden=spec.hidden, n_layers=spec.n_layers, vocab=spec.vocab, block_size=BLOCK_SIZE,
             max_tokens=max_tokens, max_seqs=max_seqs, max_pos=self.max_model_len, rms_eps=spec.rms_eps,
-            arch=L.ARCH_RAMOPEL, embed_scale=spec.embed_scale, dtype=L.DTYPE_F32 if f32 else L.DTYPE_BF16,
-            max_logit_rows=max_logit_rows, state_slots=max_seqs)
+            dtype=L.DTYPE_F32 if f32 else L.DTYPE_BF16, max_logit_rows=max_logit_rows, state_slots=max_seqs,
+            **spec.config_extras())
         descs = (L.LayerDesc * spec.n_layers)(*[ly.desc() for ly in spec.layers])
         h = C.c_void_p()
         L.check(lib.b200q_model_create_layered(C.byref(self.cfg), descs, C.byref(h)))

@@ -82,6 +82,16 @@ class RamopelSpec:
     def n_layers(self) -> int:
         return len(self.layers)
 
+    def config_extras(self) -> dict:
+        """the fields of b200q_model_config that describe this design's layer form"""
+        return dict(arch=L.ARCH_RAMOPEL, layer_form=L.FORM_PARALLEL, embed_scale=self.embed_scale)
+
+    def engine_weights(self, sd: Dict[str, torch.Tensor]) -> Iterable[Tuple[str, torch.Tensor]]:
+        return engine_weights(self, sd)
+
+    def random_checkpoint(self, seed: int = 0, device="cpu") -> Dict[str, torch.Tensor]:
+        return random_checkpoint(self, seed, device)
+
     @staticmethod
     def from_config(cfg: dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None,
                     name: str = "ramopel") -> "RamopelSpec":
