@@ -178,7 +178,10 @@ __global__ void __launch_bounds__(128) gdelta_prepare_kernel(float* __restrict__
   float* b = ba + (long long)t * 2 * heads;
   for (int h = threadIdx.x; h < heads; h += blockDim.x) {
     const float beta = sigmoidf_(b[h]);
-    const float g = expf(-expf(a_log[h]) * softplusf_(b[heads + h] + dt_bias[h]));
+    // the decay constant is the same for every token of a head: an error in exp(a_log) would add up over a
+    // sequence instead of averaging out, so this handful of values per token is evaluated in fp64
+    const double sp = (double)b[heads + h] + (double)dt_bias[h];
+    const float g = (float)exp(-exp((double)a_log[h]) * (sp > 30.0 ? sp : log1p(exp(sp))));
     b[h] = beta;
     b[heads + h] = g;
   }
@@ -391,6 +394,11 @@ __global__ void __launch_bounds__(256) chunk_attn_kernel(const float* __restrict
 // memory (they are shared by all channels).  State layout in the slot: [N][inner] (coalesced over channels).
 // ------------------------------------------------------------------------------------------------
 constexpr int SCAN_G = 8;
+// exp of a decay exponent: correctly rounded (through fp64) in the fp32 model, where a thousand decays of one
+// state entry multiply up; the fast fp32 exponential in the bf16 model
+template <typename T> __device__ __forceinline__ float decay_of(float x);
+template <> __device__ __forceinline__ float decay_of<float>(float x) { return (float)exp((double)x); }
+template <> __device__ __forceinline__ float decay_of<bf16>(float x) { return expf(x); }
 template <typename T, int NT>
 __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict__ x, const float* __restrict__ dt_raw,
                                                              const T* __restrict__ bc, int ld_bc, int b_off,
@@ -410,7 +418,8 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
   for (int n = 0; n < NT; ++n) {
     const bool in = on && n < N;
     S[n] = (in && s.pos0 > 0) ? st[(long long)n * inner + c] : 0.f;
-    A[n] = in ? -expf(a_log[(long long)c * N + n]) : 0.f;
+    // a rate is used at every token: its error would add up over a sequence, so it is rounded once, from fp64
+    A[n] = in ? -(float)exp((double)a_log[(long long)c * N + n]) : 0.f;
   }
   const float dc = on ? dvec[c] : 0.f;
   for (int g0 = 0; g0 < s.n; g0 += SCAN_G) {
@@ -431,7 +440,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
 #pragma unroll
       for (int n = 0; n < NT; ++n)
         if (n < N) {
-          S[n] = fmaf(expf(dt * A[n]), S[n], dx * Bv[n]);
+          S[n] = fmaf(decay_of<T>(dt * A[n]), S[n], dx * Bv[n]);
           y = fmaf(S[n], Cv[n], y);
         }
       y = fmaf(dc, xv, y);

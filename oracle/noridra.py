@@ -76,34 +76,43 @@ def gated_delta(h: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, mx: dict,
     return out.reshape(T, H * V) @ w[pre + "o"].T
 
 
+def sink_attention(qn: torch.Tensor, kn: torch.Tensor, val: torch.Tensor, r1: torch.Tensor, r2: torch.Tensor,
+                   scale: float, cap: float, size: int) -> torch.Tensor:
+    """qn [T, H, D] and kn [T, G, D] normed queries / keys, val [T, G, D] values -> [T, H, D].  Scores are
+    scaled, soft-capped (cap 0: not), lose r1 ln(1 + r2 (i - j)), see j <= i of the same chunk of `size`
+    positions (0: all), and the softmax carries one silent extra term of score zero in its denominator"""
+    T, H, _ = qn.shape
+    rep = H // kn.shape[1]
+    pos = torch.arange(T)
+    dist = (pos[:, None] - pos[None, :]).clamp(min=0).to(qn.dtype)
+    seen = pos[None, :] <= pos[:, None]
+    if size:
+        seen = seen & ((pos[:, None] // size) == (pos[None, :] // size))
+    out = torch.zeros_like(qn)
+    for hd in range(H):
+        s = (qn[:, hd] @ kn[:, hd // rep].T) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        s = s - r1[hd] * torch.log1p(r2[hd] * dist)
+        s = s.masked_fill(~seen, -math.inf)
+        m = s.max(-1, keepdim=True).values.clamp(min=0.0)
+        e = torch.exp(s - m)
+        p = e / (torch.exp(-m) + e.sum(-1, keepdim=True))
+        out[:, hd] = p @ val[:, hd // rep]
+    return out
+
+
 def chunk_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, mx: dict, eps: float) -> torch.Tensor:
-    """grouped-query attention whose values are the projected keys (before their norm); scores are
-    soft-capped, lose a logarithmic distance penalty per head, see only their own chunk of positions, and
-    the softmax has a silent sink of score zero"""
+    """grouped-query attention whose values are the projected keys (before their norm), with a sigmoid
+    output gate"""
     T = h.shape[0]
     H, G, D = mx["heads"], mx["kv_heads"], mx["dim"]
-    rep = H // G
     q = (h @ w[pre + "q"].T).reshape(T, H, D)
     kv = (h @ w[pre + "k"].T).reshape(T, G, D)
     qn = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * w[pre + "q.norm"]
     kn = kv / torch.sqrt((kv * kv).mean(-1, keepdim=True) + eps) * w[pre + "k.norm"]
-    pos = torch.arange(T)
-    dist = (pos[:, None] - pos[None, :]).clamp(min=0).to(h.dtype)
-    seen = pos[None, :] <= pos[:, None]
-    size = (mx.get("mask") or {}).get("size")
-    if size:
-        seen = seen & ((pos[:, None] // size) == (pos[None, :] // size))
-    cap = mx.get("softcap")
-    out = torch.zeros(T, H, D, dtype=h.dtype)
-    for hd in range(H):
-        s = (qn[:, hd] @ kn[:, hd // rep].T) * mx["scale"]
-        if cap:
-            s = cap * torch.tanh(s / cap)
-        s = s - w[pre + "r1"][hd] * torch.log1p(w[pre + "r2"][hd] * dist)
-        s = s.masked_fill(~seen, -math.inf)
-        e = torch.exp(s)                                   # scores are capped: no overflow
-        p = e / (1.0 + e.sum(-1, keepdim=True))
-        out[:, hd] = p @ kv[:, hd // rep]
+    out = sink_attention(qn, kn, kv, w[pre + "r1"], w[pre + "r2"], mx["scale"], mx.get("softcap") or 0.0,
+                         (mx.get("mask") or {}).get("size") or 0)
     gate = torch.sigmoid(h @ w[pre + "g"].T)
     return (out.reshape(T, H * D) * gate) @ w[pre + "o"].T
 
@@ -171,3 +180,13 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=torc
     if n_layers is not None:
         return x
     return group_norm(x, w["final.norm"], groups, eps) @ w["head"].T
+
+
+def greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    """greedy continuation, every step recomputed from all tokens (lowest index wins ties)"""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(torch.argmax(forward(cfg, w, toks, torch.float64)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
