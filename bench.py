@@ -691,8 +691,55 @@ def run_compare(args):
         model.close()
         return out
 
+    def decode_bytes(spec):
+        """algorithmic bytes of one decode step of a layered design (what a roofline-perfect kernel would move):
+        cache rows the attention layers read, recurrent state read and written"""
+        cache = state = 0
+        for ly in spec.layers:
+            if ly.mixer == "latent_attention":
+                cache += B * min(C0, ly.window or C0) * (ly.kv_rank + ly.rot_dim) * 2
+            elif ly.mixer == "general_delta":
+                state += B * ly.heads * ly.dim * ly.dim * 4 * 2
+            elif ly.mixer == "attention":           # keys seen at position C0: those of its own chunk
+                cache += B * (C0 % ly.chunk + 1 if ly.chunk else C0) * ly.kv_heads * ly.dim * 2
+            elif ly.mixer == "delta":
+                state += B * ly.heads * ly.dim * ly.vdim * 4 * 2
+            elif ly.mixer == "mamba1":
+                state += B * ly.inner * ly.state * 4 * 2
+        return cache, state
+
+    frac = lambda by, ms: round(by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3) if ms > 0 else None
+    tf = lambda fl, ms: round(fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 3) if ms > 0 else None
     results = {}
-    for key in args.compare_sizes.split(","):
+    if args.compare == "noridra":
+        # Noridra beside the closest existing design, Ramopel (layered, recurrent state slots, routed experts),
+        # at equal width, layer count and matrix bytes per token
+        for key in (args.compare_sizes or "noridra-1b,noridra-3b").split(","):
+            nspec, rspec = BUILTIN_SPECS[key], BUILTIN_SPECS[key.replace("noridra", "ramopel")]
+            n, r = measure(nspec), measure(rspec)
+            roof = {}
+            for name, spec, m in (("noridra", nspec, n), ("ramopel", rspec, r)):
+                cache, state = decode_bytes(spec)
+                k = m["decode"]["kernel_ms_per_step"]
+                pf = 2.0 * (spec.weight_bytes_per_token() / 2 - spec.vocab * spec.width) * n_p * S_p
+                roof[name] = {"decode_weights_of_hbm": frac(spec.weight_bytes_per_token(batch=B), k["gemm"]),
+                              "decode_attention_of_hbm": frac(cache, k["decode_attn"]),
+                              "decode_recurrence_of_hbm": frac(state, k["prefill_attn"]),
+                              "prefill_gemm_of_cublas": tf(pf, m["prefill"]["kernel_ms_per_run"]["gemm"]),
+                              "decode_cache_mb": round(cache / 1e6, 2), "decode_state_mb": round(state / 1e6, 2)}
+            results[key] = {"noridra": n, "ramopel_equal_size": r,
+                            "matrix_gb_per_token": {"noridra": round(nspec.weight_bytes_per_token() / 1e9, 3),
+                                                    "ramopel": round(rspec.weight_bytes_per_token() / 1e9, 3)},
+                            "roofline": roof}
+        print(json.dumps({"compare": "noridra", "dtype": "bf16", "data": "synthetic (random weights, random ids)",
+                          "peaks": peaks, "workload": {"prefill": f"{n_p} prompts x {S_p} tokens",
+                                                       "decode": f"{B} sequences at context {C0}"},
+                          "units": "decode_*_of_hbm: fraction of the measured HBM copy bandwidth (bytes a step must move / "
+                                   "device time of the kernel category; recurrence = delta rules and scans, attention = "
+                                   "cache readers); prefill_gemm_of_cublas: matrix flops / gemm time over measured cuBLAS bf16",
+                          "results": results}))
+        return
+    for key in (args.compare_sizes or "ramopel-1b,ramopel-3b").split(","):
         rspec = BUILTIN_SPECS[key]
         lspec = llama_of_equal_size(rspec)
         wb = rspec.weight_bytes_per_token()
@@ -706,7 +753,6 @@ def run_compare(args):
         state_r = B * d0.heads * d0.dim * d0.dim * 4 * 2 * n_delta
         cache_l = B * C0 * 2 * lspec.n_kv_heads * lspec.head_dim * 2 * lspec.n_layers
         rk, lk = r["decode"]["kernel_ms_per_step"], l["decode"]["kernel_ms_per_step"]
-        frac = lambda by, ms: round(by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3) if ms > 0 else None
         roof = {
             "decode_weights": {"ramopel": frac(rspec.weight_bytes_per_token(batch=B), rk["gemm"]),
                                "llama": frac(lspec.weight_bytes_per_step() - 2 * lspec.vocab * lspec.hidden, lk["gemm"]),
@@ -720,7 +766,6 @@ def run_compare(args):
         }
         pf = 2.0 * (wb / 2 - rspec.vocab * rspec.width) * n_p * S_p       # matrix flops of the prefill (no lm head)
         pfl = 2.0 * (lspec.weight_bytes_per_step() / 2 - 2 * lspec.vocab * lspec.hidden) * n_p * S_p
-        tf = lambda fl, ms: round(fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 3) if ms > 0 else None
         roof["prefill_gemm"] = {"ramopel": tf(pf, r["prefill"]["kernel_ms_per_run"]["gemm"]),
                                 "llama": tf(pfl, l["prefill"]["kernel_ms_per_run"]["gemm"]),
                                 "unit": "fraction of measured cuBLAS bf16 throughput, matrix flops / gemm time"}
@@ -756,10 +801,11 @@ def main():
     ap.add_argument("--cpu-budget-s", type=float, default=10.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dry-run", action="store_true", help="host-logic self-test without a GPU (not a measurement)")
-    ap.add_argument("--compare", default=None, choices=["ramopel"],
-                    help="instead of the headline workload: prefill / decode throughput of this design beside a Llama "
-                         "decoder of equal size (random weights), one JSON line")
-    ap.add_argument("--compare-sizes", default="ramopel-1b,ramopel-3b")
+    ap.add_argument("--compare", default=None, choices=["ramopel", "noridra"],
+                    help="instead of the headline workload: prefill / decode throughput of this design beside the closest "
+                         "existing model of equal size (ramopel: a Llama decoder; noridra: Ramopel), random weights, one "
+                         "JSON line")
+    ap.add_argument("--compare-sizes", default=None, help="builtin sizes, default <design>-1b,<design>-3b")
     ap.add_argument("--compare-prompt", type=int, default=2048)
     ap.add_argument("--compare-prompts", type=int, default=4)
     ap.add_argument("--compare-batch", type=int, default=128)

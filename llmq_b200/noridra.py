@@ -309,6 +309,6 @@ def _cycle(width: int, vocab: int, n_layers: int, heads: int, kv_heads: int, dim
 
 # sizes that resemble a real model's layers (random weights; `random:<name>` as a model name)
 BUILTIN_SPECS = {
-    "noridra-1b": _cycle(2048, 32768, 16, 16, 4, 128, 32, 4, 1024, "noridra-1b"),
-    "noridra-3b": _cycle(3072, 32768, 24, 24, 8, 128, 64, 6, 1536, "noridra-3b"),
+    "noridra-1b": _cycle(2048, 32768, 16, 16, 4, 128, 16, 4, 1024, "noridra-1b"),
+    "noridra-3b": _cycle(3072, 32768, 24, 24, 8, 128, 32, 6, 1536, "noridra-3b"),
 }
