@@ -340,11 +340,12 @@ int b200q_chunk_attn(const float* qs_dev, const void* cache_dev, const int32_t* 
                      const float* r2_dev, const void* gate_dev, int ld_gate, float eps, void* out_dev, int dtype,
                      void* stream);
 /* selective scan.  x: model dtype [T, inner] (after convolution and SiLU); dt_raw: fp32 [T, inner] (before
- * softplus, bias included); bc: model dtype rows (ld_bc) whose entries [b_off, b_off + N) are B and
+ * softplus), dt_bias: fp32 [inner] added to it (NULL: none); bc: model dtype rows (ld_bc) whose entries [b_off, b_off + N) are B and
  * [b_off + N, b_off + 2N) are C; z: model dtype rows (ld_z); a_log: fp32 [inner, N]; d: fp32 [inner].
- *   dt = softplus(dt_raw);  S[c,n] <- exp(dt_c * -exp(a_log[c,n])) S[c,n] + dt_c x_c B_n;
+ *   dt = softplus(dt_raw + dt_bias);  S[c,n] <- exp(dt_c * -exp(a_log[c,n])) S[c,n] + dt_c x_c B_n;
  *   y_c = sum_n S[c,n] C_n + d_c x_c;  out = y * silu(z).     state: fp32 [inner][N] per slot. */
-int b200q_selective_scan(const void* x_dev, const float* dt_raw_dev, const void* bc_dev, int ld_bc, int b_off,
+int b200q_selective_scan(const void* x_dev, const float* dt_raw_dev, const float* dt_bias_dev, const void* bc_dev,
+                         int ld_bc, int b_off,
                          const void* z_dev, int ld_z, const float* a_log_dev, const float* d_dev, float* state_dev,
                          long long slot_stride, const int32_t* seq_desc_dev, int n_seqs, int inner, int N,
                          void* out_dev, int dtype, void* stream);

@@ -124,7 +124,7 @@ Widths widths_of(const b200q_model_config& c, const std::vector<b200q_layered_la
     } else if (d.mixer == B200Q_MIXER_SELECTIVE_SCAN) {
       w.proj = std::max<int64_t>(w.proj, 2 * (int64_t)d.inner);
       w.xc = std::max<int64_t>(w.xc, d.inner);
-      w.xp = std::max<int64_t>(w.xp, d.dt_rank + 2 * (int64_t)d.state_dim);
+      w.xp = std::max<int64_t>(w.xp, (d.dt_rank + 2 * (int64_t)d.state_dim + 63) & ~(int64_t)63);
       w.dtr = std::max<int64_t>(w.dtr, d.inner);
       w.attn = std::max<int64_t>(w.attn, d.inner);
     }
@@ -357,7 +357,7 @@ int layered_bind_weight(b200q_model* m, const char* name, const void* p, int64_t
     FIELD("mix.proj", l.proj, 2 * d.inner, W)
     FIELD("mix.conv", l.conv_w, 1, (int64_t)d.inner * d.conv_taps)
     FIELD("mix.conv_b", l.conv_b, 1, d.inner)
-    FIELD("mix.x", l.x_proj, d.dt_rank + 2 * d.state_dim, d.inner)
+    FIELD("mix.x", l.x_proj, (d.dt_rank + 2 * d.state_dim + 63) & ~63, d.inner)  // zero rows up to a multiple of 64
     FIELD("mix.dt", l.dt_proj, d.inner, d.dt_rank)
     FIELD("mix.dt_b", l.dt_b, 1, d.inner)
     FIELD("mix.a_log", l.a_log, 1, (int64_t)d.inner * d.state_dim)
@@ -559,16 +559,18 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
                            d.chunk, d.attn_scale, d.softcap, l.r1, l.r2, gate, NP, c.rms_eps, y->attn, dt, stream));
       LIN(y->attn, HD, l.o, nullptr, y->mix, W, W, HD, 0);
     } else {  // B200Q_MIXER_SELECTIVE_SCAN
-      const int I = d.inner, N = d.state_dim, R = d.dt_rank, NX = R + 2 * N;
+      // the rows of the [dt | B | C] projection are padded with zero rows to a multiple of 64 at load time, so
+      // that both small projections take the tensor-core path whenever the other sizes allow it
+      const int I = d.inner, N = d.state_dim, R = d.dt_rank, NX = (R + 2 * N + 63) & ~63;
       LIN(y->h1, W, l.proj, nullptr, y->proj, 2 * I, 2 * I, W, 0);    // [x | z]
       TRY(EW, 2.0 * T * I * es,
           b200q_causal_conv(y->proj, 2 * I, 0, l.conv_w, l.conv_b, I, d.conv_taps, 1, 0, y->state + l.conv_off,
                             y->state_slot_floats, b->seq_desc, b->row_seq, b->n_rows, y->xc, I, 0, T, dt, stream));
       LIN(y->xc, I, l.x_proj, nullptr, y->xp, NX, NX, I, 0);          // [dt | B | C]
-      LIN(y->xp, NX, l.dt_proj, l.dt_b, y->dtr, I, I, R, 1);          // step sizes before softplus, fp32
+      LIN(y->xp, NX, l.dt_proj, nullptr, y->dtr, I, I, R, 1);         // step sizes before bias and softplus, fp32
       uint8_t* z = (uint8_t*)y->proj + (size_t)I * es;
       TRY(B200Q_PROF_PREFILL_ATTN, 8.0 * b->n_rows * (double)I * N,
-          b200q_selective_scan(y->xc, y->dtr, y->xp, NX, R, z, 2 * I, l.a_log, l.dvec, y->state + l.state_off,
+          b200q_selective_scan(y->xc, y->dtr, l.dt_b, y->xp, NX, R, z, 2 * I, l.a_log, l.dvec, y->state + l.state_off,
                                y->state_slot_floats, b->seq_desc, b->n_rows, I, N, y->attn, dt, stream));
       LIN(y->attn, I, l.o, nullptr, y->mix, W, W, I, 0);
     }

@@ -154,9 +154,8 @@ __global__ void __launch_bounds__(256) conv_state_kernel(const TI* __restrict__ 
 // gated delta rule, three launches.
 //   prepare (CTA per token): q, k -> unit vectors per head (q also times dim^-1/2), in place in the fp32
 //           qkv rows; ba row (beta logits | decay inputs) -> (beta | g) in place
-//   recur   (CTA per sequence x head, thread j = value column j, the state column S[0..dim) in registers):
+//   recur   (one warp per sequence x head x 32 value columns, lane j = column j, S[0..dim) in registers):
 //           S <- g S;  u = beta (v_j - k.S);  S <- S + k u;  o_j = q.S   -> raw [T, heads*vdim] (fp32)
-//           k, q, beta, g of 8 tokens at a time are staged in shared memory
 //   finish  (CTA per token x head): out = raw / rms(raw) * out_norm * silu(gate)
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) gdelta_prepare_kernel(float* __restrict__ qkv, float* __restrict__ ba,
@@ -187,58 +186,106 @@ __global__ void __launch_bounds__(128) gdelta_prepare_kernel(float* __restrict__
   }
 }
 
-constexpr int GDELTA_G = 8;  // tokens staged per barrier pair
+// One warp per (sequence, head, 32 value columns): columns are independent, so a head's state is spread over
+// vdim/32 CTAs.  Lane j keeps column j of the state (dim values, zero-padded to DT) in registers; k and q of 8
+// tokens at a time arrive in shared memory by cp.async one group ahead of the one being consumed, v of the
+// group is prefetched into registers, and both dot products run as four independent FMA chains.
+constexpr int GDELTA_G = 8;
+__device__ __forceinline__ void cp_async16_(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
 template <int DT>
-__global__ void gdelta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ bg,
-                                    float* __restrict__ state, long long slot_stride,
-                                    const int32_t* __restrict__ seq_desc, int heads, int kv_heads, int dim, int vdim,
-                                    float* __restrict__ raw) {
-  extern __shared__ float sm[];
-  float* kq = sm;                           // [G][2*dim]: k then q of the token
-  float* bgs = sm + GDELTA_G * 2 * dim;     // [G][2]
+__global__ void __launch_bounds__(32) gdelta_recur_kernel(const float* __restrict__ qkv, const float* __restrict__ bg,
+                                                          float* __restrict__ state, long long slot_stride,
+                                                          const int32_t* __restrict__ seq_desc, int heads, int kv_heads,
+                                                          int dim, int vdim, float* __restrict__ raw) {
+  extern __shared__ __align__(16) float sm[];  // [2][G][2*DT]: k (padded to DT) then q (padded to DT)
   const SeqView s = seq_view(seq_desc, blockIdx.x);
-  const int h = blockIdx.y, j = threadIdx.x, kvh = h / (heads / kv_heads);
+  const int h = blockIdx.y, lane = threadIdx.x, j = blockIdx.z * 32 + lane, kvh = h / (heads / kv_heads);
   const int GD = kv_heads * dim, ldq = 2 * GD + heads * vdim, HV = heads * vdim;
   const bool on = j < vdim;
+  // 16-byte copies need every k and q vector to start on a 16-byte boundary: head size, row stride and base
+  const bool vec = (dim & 3) == 0 && (ldq & 3) == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0;
   float* st = state + (long long)s.slot * slot_stride + (long long)h * dim * vdim;
+  for (int e = lane; e < 2 * GDELTA_G * 2 * DT; e += 32) sm[e] = 0.f;  // the padding stays zero
+  __syncwarp();
+  auto fetch = [&](int g0, int buf) {
+    const int cnt = min(GDELTA_G, s.n - g0);
+    float* dst0 = sm + (long long)buf * GDELTA_G * 2 * DT;
+    if (vec) {
+      const int per = dim / 2;  // 16-byte pieces of one token: dim/4 of k, dim/4 of q
+      for (int e = lane; e < cnt * per; e += 32) {
+        const int tk = e / per, pc = e % per;
+        const float* r = qkv + (long long)(s.row0 + g0 + tk) * ldq + kvh * dim;
+        const bool isq = pc >= dim / 4;
+        const int off = (isq ? pc - dim / 4 : pc) * 4;
+        cp_async16_(dst0 + tk * 2 * DT + (isq ? DT : 0) + off, r + (isq ? 0 : GD) + off);
+      }
+    } else {
+      for (int e = lane; e < cnt * 2 * dim; e += 32) {
+        const int tk = e / (2 * dim), i = e % (2 * dim);
+        const float* r = qkv + (long long)(s.row0 + g0 + tk) * ldq + kvh * dim;
+        dst0[tk * 2 * DT + (i < dim ? i : DT + i - dim)] = i < dim ? r[GD + i] : r[i - dim];
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch(0, 0);
   float S[DT];
 #pragma unroll
   for (int q = 0; q < DT; ++q) S[q] = (on && q < dim && s.pos0 > 0) ? st[(long long)q * vdim + j] : 0.f;
-  for (int g0 = 0; g0 < s.n; g0 += GDELTA_G) {
+  for (int g0 = 0, buf = 0; g0 < s.n; g0 += GDELTA_G, buf ^= 1) {
     const int cnt = min(GDELTA_G, s.n - g0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < cnt * 2 * dim; e += blockDim.x) {
-      const int tk = e / (2 * dim), i = e % (2 * dim);
-      const float* r = qkv + (long long)(s.row0 + g0 + tk) * ldq;
-      kq[e] = i < dim ? r[GD + kvh * dim + i] : r[kvh * dim + i - dim];
-    }
-    for (int e = threadIdx.x; e < cnt * 2; e += blockDim.x) {
-      const int tk = e >> 1;
-      bgs[e] = bg[(long long)(s.row0 + g0 + tk) * 2 * heads + (e & 1) * heads + h];
-    }
-    __syncthreads();
-    if (!on) continue;
-    for (int tk = 0; tk < cnt; ++tk) {
-      const long long r = s.row0 + g0 + tk;
-      const float* kk = kq + tk * 2 * dim;
-      const float* qq = kk + dim;
-      const float beta = bgs[2 * tk], g = bgs[2 * tk + 1], vj = qkv[r * ldq + 2 * GD + h * vdim + j];
-      float kS = 0.f;
+    float vj[GDELTA_G];
 #pragma unroll
-      for (int q = 0; q < DT; ++q)
-        if (q < dim) {
-          S[q] *= g;
-          kS = fmaf(kk[q], S[q], kS);
-        }
-      const float u = beta * (vj - kS);
-      float o = 0.f;
+    for (int tk = 0; tk < GDELTA_G; ++tk)
+      vj[tk] = (on && tk < cnt) ? qkv[(long long)(s.row0 + g0 + tk) * ldq + 2 * GD + h * vdim + j] : 0.f;
+    // lane tk holds (beta, g) of token tk of the group
+    float my_b = 0.f, my_g = 1.f;
+    if (lane < cnt) {
+      const float* b = bg + (long long)(s.row0 + g0 + lane) * 2 * heads;
+      my_b = b[h];
+      my_g = b[heads + h];
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();  // this group has landed; the other buffer is no longer read
+    if (g0 + GDELTA_G < s.n) fetch(g0 + GDELTA_G, buf ^ 1);
+    const float* base = sm + (long long)buf * GDELTA_G * 2 * DT;
 #pragma unroll
-      for (int q = 0; q < DT; ++q)
-        if (q < dim) {
-          S[q] = fmaf(kk[q], u, S[q]);
-          o = fmaf(S[q], qq[q], o);
+    for (int tk = 0; tk < GDELTA_G; ++tk) {
+      if (tk < cnt) {
+        const float beta = __shfl_sync(0xffffffffu, my_b, tk), g = __shfl_sync(0xffffffffu, my_g, tk);
+        const float4* k4 = reinterpret_cast<const float4*>(base + tk * 2 * DT);
+        const float4* q4 = k4 + DT / 4;
+        float u0 = 0.f, u1 = 0.f, u2 = 0.f, u3 = 0.f;
+#pragma unroll
+        for (int q = 0; q < DT / 4; ++q) {
+          const float4 k = k4[q];
+          S[4 * q] *= g;
+          S[4 * q + 1] *= g;
+          S[4 * q + 2] *= g;
+          S[4 * q + 3] *= g;
+          u0 = fmaf(k.x, S[4 * q], u0);
+          u1 = fmaf(k.y, S[4 * q + 1], u1);
+          u2 = fmaf(k.z, S[4 * q + 2], u2);
+          u3 = fmaf(k.w, S[4 * q + 3], u3);
         }
-      raw[r * HV + h * vdim + j] = o;
+        const float u = beta * (vj[tk] - ((u0 + u1) + (u2 + u3)));
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+        for (int q = 0; q < DT / 4; ++q) {
+          const float4 k = k4[q], qq = q4[q];
+          S[4 * q] = fmaf(k.x, u, S[4 * q]);
+          S[4 * q + 1] = fmaf(k.y, u, S[4 * q + 1]);
+          S[4 * q + 2] = fmaf(k.z, u, S[4 * q + 2]);
+          S[4 * q + 3] = fmaf(k.w, u, S[4 * q + 3]);
+          o0 = fmaf(S[4 * q], qq.x, o0);
+          o1 = fmaf(S[4 * q + 1], qq.y, o1);
+          o2 = fmaf(S[4 * q + 2], qq.z, o2);
+          o3 = fmaf(S[4 * q + 3], qq.w, o3);
+        }
+        if (on) raw[(long long)(s.row0 + g0 + tk) * HV + h * vdim + j] = (o0 + o1) + (o2 + o3);
+      }
     }
   }
   if (on) {
@@ -401,6 +448,7 @@ template <> __device__ __forceinline__ float decay_of<float>(float x) { return (
 template <> __device__ __forceinline__ float decay_of<bf16>(float x) { return expf(x); }
 template <typename T, int NT>
 __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict__ x, const float* __restrict__ dt_raw,
+                                                             const float* __restrict__ dt_bias,
                                                              const T* __restrict__ bc, int ld_bc, int b_off,
                                                              const T* __restrict__ z, int ld_z,
                                                              const float* __restrict__ a_log,
@@ -421,7 +469,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
     // a rate is used at every token: its error would add up over a sequence, so it is rounded once, from fp64
     A[n] = in ? -(float)exp((double)a_log[(long long)c * N + n]) : 0.f;
   }
-  const float dc = on ? dvec[c] : 0.f;
+  const float dc = on ? dvec[c] : 0.f, dtb = (on && dt_bias) ? dt_bias[c] : 0.f;
   for (int g0 = 0; g0 < s.n; g0 += SCAN_G) {
     const int cnt = min(SCAN_G, s.n - g0);
     __syncthreads();
@@ -435,7 +483,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
       const long long r = s.row0 + g0 + tk;
       const float* Bv = sm + tk * 2 * N;
       const float* Cv = Bv + N;
-      const float dt = softplusf_(dt_raw[r * inner + c]), xv = ldf(x + r * inner + c), dx = dt * xv;
+      const float dt = softplusf_(dt_raw[r * inner + c] + dtb), xv = ldf(x + r * inner + c), dx = dt * xv;
       float y = 0.f;
 #pragma unroll
       for (int n = 0; n < NT; ++n)
@@ -565,11 +613,13 @@ int b200q_gated_delta(float* qkv, float* ba, float* raw, const void* gate, int l
   gdelta_prepare_kernel<<<T_, 128, 0, st>>>(q, b, a_log, dt_bias, heads, kv_heads, dim, vdim);
   B200Q_LAUNCH_CHECK();
   const int threads = (vdim + 31) & ~31;
-  const size_t smem = (size_t)GDELTA_G * (2 * dim + 2) * sizeof(float);
-  dim3 grid(n_seqs, heads);
+  dim3 grid(n_seqs, heads, (vdim + 31) / 32);
 #define RECUR(DT)                                                                                                  \
-  gdelta_recur_kernel<DT><<<grid, threads, smem, st>>>(q, b, state, slot_stride, seq_desc, heads, kv_heads, dim, \
-                                                       vdim, raw)
+  do {                                                                                                             \
+    const size_t smem = (size_t)2 * GDELTA_G * 2 * DT * sizeof(float);                                             \
+    gdelta_recur_kernel<DT><<<grid, 32, smem, st>>>(q, b, state, slot_stride, seq_desc, heads, kv_heads, dim, vdim, \
+                                                    raw);                                                          \
+  } while (0)
   if (dim <= 32) RECUR(32);
   else if (dim <= 64) RECUR(64);
   else if (dim <= 128) RECUR(128);
@@ -632,7 +682,8 @@ int b200q_chunk_attn(const float* qs, const void* cache, const int32_t* block_ta
   return B200Q_OK;
 }
 
-int b200q_selective_scan(const void* x, const float* dt_raw, const void* bc, int ld_bc, int b_off, const void* z,
+int b200q_selective_scan(const void* x, const float* dt_raw, const float* dt_bias, const void* bc, int ld_bc, int b_off,
+                         const void* z,
                          int ld_z, const float* a_log, const float* d, float* state, long long slot_stride,
                          const int32_t* seq_desc, int n_seqs, int inner, int N, void* out, int dtype, void* stream) {
   B200Q_CHECK_ARG(x && dt_raw && bc && z && a_log && d && state && seq_desc && out && inner > 0 && N > 0 && N <= 256 &&
@@ -643,7 +694,8 @@ int b200q_selective_scan(const void* x, const float* dt_raw, const void* bc, int
   const size_t smem = (size_t)SCAN_G * 2 * N * sizeof(float);
 #define SCAN(TT, NT)                                                                                              \
   selective_scan_kernel<TT, NT><<<grid, 128, smem, as_stream(stream)>>>(                                          \
-      (const TT*)x, dt_raw, (const TT*)bc, ld_bc, b_off, (const TT*)z, ld_z, a_log, d, state, slot_stride, seq_desc, \
+      (const TT*)x, dt_raw, dt_bias, (const TT*)bc, ld_bc, b_off, (const TT*)z, ld_z, a_log, d, state, slot_stride,  \
+      seq_desc,                                                                                                     \
       inner, N, (TT*)out)
 #define SCAN_BY_N(TT)                 \
   do {                                \

@@ -213,7 +213,9 @@ def engine_weights(spec: NoridraSpec, sd: Dict[str, torch.Tensor]) -> Iterable[T
             yield o + "mix.proj", sd[m + "in"]
             yield o + "mix.conv", sd[m + "conv"].reshape(-1)
             yield o + "mix.conv_b", sd[m + "conv.b"]
-            yield o + "mix.x", sd[m + "x"]
+            xw = sd[m + "x"]                       # [dt | B | C] rows, padded with zero rows to a multiple of 64
+            pad = -xw.shape[0] % 64
+            yield o + "mix.x", (torch.cat([xw, xw.new_zeros(pad, xw.shape[1])], 0) if pad else xw)
             yield o + "mix.dt", sd[m + "dt"]
             yield o + "mix.dt_b", sd[m + "dt.b"]
             yield o + "mix.a_log", sd[m + "A_log"].reshape(-1)
