@@ -339,6 +339,14 @@ int b200q_chunk_attn(const float* qs_dev, const void* cache_dev, const int32_t* 
                      int dim, int block_size, int chunk, float scale, float softcap, const float* r1_dev,
                      const float* r2_dev, const void* gate_dev, int ld_gate, float eps, void* out_dev, int dtype,
                      void* stream);
+/* the same with the per-sequence view of the step (seq_desc / n_seqs; row r of the block table is sequence r):
+ * bf16 caches with a head size of 64 or 128 then run on the tensor cores, 16 consecutive tokens of a sequence per
+ * tile (results equal the form above up to rounding: the queries and the softmax weights are rounded to bf16) */
+int b200q_chunk_attn_seq(const float* qs_dev, const void* cache_dev, const int32_t* block_table_dev, int bt_stride,
+                         const int32_t* row_seq_dev, const int32_t* positions_dev, const int32_t* seq_desc_dev,
+                         int n_seqs, int T, int heads, int kv_heads, int dim, int block_size, int chunk, float scale,
+                         float softcap, const float* r1_dev, const float* r2_dev, const void* gate_dev, int ld_gate,
+                         float eps, void* out_dev, int dtype, void* stream);
 /* selective scan.  x: model dtype [T, inner] (after convolution and SiLU); dt_raw: fp32 [T, inner] (before
  * softplus), dt_bias: fp32 [inner] added to it (NULL: none); bc: model dtype rows (ld_bc) whose entries [b_off, b_off + N) are B and
  * [b_off + N, b_off + 2N) are C; z: model dtype rows (ld_z); a_log: fp32 [inner, N]; d: fp32 [inner].

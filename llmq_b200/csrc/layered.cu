@@ -555,8 +555,9 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
                                 stream));
       uint8_t* gate = (uint8_t*)y->proj + (size_t)(HD + G * D) * es;
       TRY(B200Q_PROF_DECODE_ATTN, (double)b->sum_ctx_dec * G * D * es,
-          b200q_chunk_attn(y->qa, cache, b->block_table, b->bt_stride, b->row_seq, b->positions, T, H, G, D, c.block_size,
-                           d.chunk, d.attn_scale, d.softcap, l.r1, l.r2, gate, NP, c.rms_eps, y->attn, dt, stream));
+          b200q_chunk_attn_seq(y->qa, cache, b->block_table, b->bt_stride, b->row_seq, b->positions, b->seq_desc,
+                               b->n_rows, T, H, G, D, c.block_size, d.chunk, d.attn_scale, d.softcap, l.r1, l.r2, gate, NP,
+                               c.rms_eps, y->attn, dt, stream));
       LIN(y->attn, HD, l.o, nullptr, y->mix, W, W, HD, 0);
     } else {  // B200Q_MIXER_SELECTIVE_SCAN
       // the rows of the [dt | B | C] projection are padded with zero rows to a multiple of 64 at load time, so

@@ -11,6 +11,8 @@
 // Every reduction has a fixed order per row and every loop over keys or tokens starts at a place that
 // depends only on the token's position in its sequence (chunk start, sequence start), so a token's result
 // does not depend on how its prompt was cut into steps, on its batch-mates, or on pages and slots.
+#include <stdlib.h>
+
 #include "layered_common.cuh"
 
 namespace b200q {
@@ -436,6 +438,208 @@ __global__ void __launch_bounds__(256) chunk_attn_kernel(const float* __restrict
 }
 
 // ------------------------------------------------------------------------------------------------
+// chunk attention on the tensor cores (bf16 cache, head size 64 or 128).  One CTA per (sequence of the step,
+// key/value head, tile of 16 consecutive tokens of the sequence's portion); warp w serves query head w of the
+// group, the 16 tokens are the M rows of mma.sync.m16n8k16 tiles.  Key tiles of 64 cached rows arrive by
+// cp.async into a double-buffered shared-memory tile that all heads of the group read twice: as keys
+// (S = Q K^T, then times 1/rms(k) per key, scale, soft cap, distance penalty, chunk and causal mask) and, through
+// ldmatrix.trans, as values (O += P K).  Online softmax in fp32 registers starting from the sink's state
+// (maximum 0, denominator 1); the weights are rounded to bf16 before they are summed, as the value product
+// sees them.  A decoded token is a tile with one live row.  Key tiles start at the chunk start of the tile's
+// first token.
+// ------------------------------------------------------------------------------------------------
+constexpr int CATT_KEYS = 64;
+template <int D>
+__global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __restrict__ qs, const bf16* __restrict__ cache,
+                                                             const int32_t* __restrict__ block_table, int bt_stride,
+                                                             const int32_t* __restrict__ seq_desc, int heads,
+                                                             int kv_heads, int block_size, int chunk, float scale,
+                                                             float softcap, const float* __restrict__ r1,
+                                                             const float* __restrict__ r2, const bf16* __restrict__ gate,
+                                                             int ld_gate, float eps, bf16* __restrict__ out) {
+  constexpr int LDS = D + 8;  // padded row (bf16 elements): ldmatrix rows fall on different banks
+  extern __shared__ __align__(16) uint8_t smraw[];
+  const int nw = blockDim.x >> 5;
+  bf16* qsm = reinterpret_cast<bf16*>(smraw);                 // [nw][16][LDS]
+  bf16* kbuf = qsm + (long long)nw * 16 * LDS;                // [2][64][LDS]
+  float* kinv = reinterpret_cast<float*>(kbuf + 2 * CATT_KEYS * LDS);  // [2][64]
+  const SeqView sq = seq_view(seq_desc, blockIdx.x);
+  const int r0 = blockIdx.z * 16;
+  if (r0 >= sq.n) return;
+  const int nrows = min(16, sq.n - r0);
+  const int rep = heads / kv_heads, parts = (rep + nw - 1) / nw;
+  const int g = blockIdx.y / parts, part = blockIdx.y % parts;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q4 = lane & 3;
+  const int hg = part * nw + warp;
+  const bool live = hg < rep;
+  const int h = g * rep + (live ? hg : 0);
+  const int p_first = sq.pos0 + r0, p_last = p_first + nrows - 1;
+  const int lo_first = chunk > 0 ? p_first - p_first % chunk : 0;
+  const int32_t* bt = block_table + (long long)blockIdx.x * bt_stride;
+  const int GD = kv_heads * D;
+  const int ntiles = (p_last - lo_first) / CATT_KEYS + 1;
+
+  auto load_tile = [&](int c, int buf) {
+    const int j0 = lo_first + c * CATT_KEYS;
+    bf16* kb = kbuf + (long long)buf * CATT_KEYS * LDS;
+    constexpr int CPR = D / 8;  // 16-byte pieces of a key row
+    for (int e = tid; e < CATT_KEYS * CPR; e += blockDim.x) {
+      const int j = e / CPR, ck = e % CPR, pos = j0 + j;
+      bf16* dst = kb + j * LDS + ck * 8;
+      if (pos <= p_last) {
+        const long long row = (long long)bt[pos / block_size] * block_size + pos % block_size;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
+                     "l"(cache + row * GD + (long long)g * D + ck * 8)
+                     : "memory");
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  load_tile(0, 0);
+  // the queries of this CTA's heads (norm weights folded in), bf16, rows past the portion are zeros
+  for (int e = tid; e < nw * 16 * D; e += blockDim.x) {
+    const int w = e / (16 * D), r = (e / D) % 16, d = e % D, hh = part * nw + w;
+    const float v = (hh < rep && r < nrows) ? qs[((long long)(sq.row0 + r0 + r) * heads + g * rep + hh) * D + d] : 0.f;
+    qsm[((long long)w * 16 + r) * LDS + d] = __float2bfloat16_rn(v);
+  }
+  const uint32_t q_s = smem_u32(qsm + (long long)warp * 16 * LDS);
+  const uint32_t a_off = (uint32_t)(((lane & 15) * LDS + (lane >> 4) * 8) * 2);
+  const uint32_t kq_off = (uint32_t)((((lane & 7) + 8 * (lane >> 4)) * LDS + 8 * ((lane >> 3) & 1)) * 2);
+  const float c1 = r1[h], c2 = r2[h];
+  // rows gq and gq + 8 of the tile belong to this thread
+  int p_row[2], lo_row[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = gq + 8 * r;
+    p_row[r] = i < nrows ? p_first + i : -1;  // a dead row sees no key
+    lo_row[r] = (chunk > 0 && i < nrows) ? p_row[r] - p_row[r] % chunk : 0;
+  }
+  float m_[2] = {0.f, 0.f}, l_[2] = {q4 == 0 ? 1.f : 0.f, q4 == 0 ? 1.f : 0.f};  // the sink, counted once per row
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int c = 0; c < ntiles; ++c) {
+    const int buf = c & 1, j0 = lo_first + c * CATT_KEYS;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // tile c (and, first time, the queries) is in shared memory; tile c-1 is done with
+    if (c + 1 < ntiles) load_tile(c + 1, buf ^ 1);
+    const bf16* kb = kbuf + (long long)buf * CATT_KEYS * LDS;
+    float* kiv = kinv + buf * CATT_KEYS;
+    for (int j = warp; j < CATT_KEYS; j += nw) {  // 1/rms of every key of the tile, fixed order
+      float ss = 0.f;
+#pragma unroll
+      for (int d = lane; d < D; d += 32) {
+        const float v = __bfloat162float(kb[j * LDS + d]);
+        ss = fmaf(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) kiv[j] = 1.f / sqrtf(ss / (float)D + eps);
+    }
+    __syncthreads();
+    if (!live) continue;
+    const uint32_t kb_s = smem_u32(kb);
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldsm_x4(q_s + a_off + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+      for (int nt2 = 0; nt2 < 4; ++nt2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(kb_s + kq_off + (uint32_t)(nt2 * 16 * LDS * 2 + ks * 32), b0, b1, b2, b3);
+        mma_bf16_16816(s[2 * nt2], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(s[2 * nt2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    // ---- scores -> capped, penalised, masked; online softmax over the tile ----
+    float rmax[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kk = nt * 8 + 2 * q4 + (e & 1), j = j0 + kk, r = e >> 1;
+        float v = -INFINITY;
+        if (j <= p_row[r] && j >= lo_row[r]) {
+          v = s[nt][e] * kiv[kk] * scale;
+          if (softcap > 0.f) v = softcap * tanhf(v / softcap);
+          v -= c1 * log1pf(c2 * (float)(p_row[r] - j));
+        }
+        s[nt][e] = v;
+        rmax[r] = fmaxf(rmax[r], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 1));
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 2));
+      const float mn = fmaxf(m_[r], rmax[r]);
+      corr[r] = expf(m_[r] - mn);
+      m_[r] = mn;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = round_bf16(expf(s[nt][e] - m_[e >> 1]));  // masked: exp(-inf) = 0
+        s[nt][e] = pv;
+        psum[e >> 1] += pv;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_[r] = l_[r] * corr[r] + psum[r];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+    // ---- O += P V, the values being the raw keys of the same tile ----
+#pragma unroll
+    for (int kk2 = 0; kk2 < CATT_KEYS / 16; ++kk2) {
+      const uint32_t a0 = pack_bf16x2(s[2 * kk2][0], s[2 * kk2][1]), a1 = pack_bf16x2(s[2 * kk2][2], s[2 * kk2][3]);
+      const uint32_t a2 = pack_bf16x2(s[2 * kk2 + 1][0], s[2 * kk2 + 1][1]),
+                     a3 = pack_bf16x2(s[2 * kk2 + 1][2], s[2 * kk2 + 1][3]);
+      const int key = kk2 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const uint32_t v_row = kb_s + (uint32_t)((key * LDS + 8 * (lane >> 4)) * 2);
+#pragma unroll
+      for (int nd2 = 0; nd2 < D / 16; ++nd2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(v_row + nd2 * 32, b0, b1, b2, b3);
+        mma_bf16_16816(o[2 * nd2], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(o[2 * nd2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+  }
+  if (!live) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_[r] += __shfl_xor_sync(0xffffffffu, l_[r], 1);
+    l_[r] += __shfl_xor_sync(0xffffffffu, l_[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = gq + 8 * r;
+    if (i >= nrows) continue;
+    const long long t = sq.row0 + r0 + i;
+    const float inv = 1.f / l_[r];
+    const bf16* gr = gate + t * ld_gate + (long long)h * D;
+    bf16* orow = out + (t * heads + h) * D;
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+      const int d = nt * 8 + 2 * q4;
+      const float g0 = sigmoidf_(__bfloat162float(gr[d])), g1 = sigmoidf_(__bfloat162float(gr[d + 1]));
+      *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16x2(o[nt][2 * r] * inv * g0, o[nt][2 * r + 1] * inv * g1);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // selective scan: one CTA per (sequence, 128 channels), thread = channel, the channel's state S[0..N) and
 // its decay rates A[n] = -exp(a_log) in registers; B and C of 8 tokens at a time are staged in shared
 // memory (they are shared by all channels).  State layout in the slot: [N][inner] (coalesced over channels).
@@ -646,16 +850,57 @@ int b200q_chunk_attn_prep(const void* proj, int ldp, int heads, int kv_heads, in
   return B200Q_OK;
 }
 
+static int chunk_attn_mma_mode() {  // B200Q_CHUNK_ATTN_MMA=0: the scalar kernel everywhere
+  static const int mode = [] {
+    const char* v = getenv("B200Q_CHUNK_ATTN_MMA");
+    return v ? atoi(v) : 1;
+  }();
+  return mode;
+}
+
 int b200q_chunk_attn(const float* qs, const void* cache, const int32_t* block_table, int bt_stride,
                      const int32_t* row_seq, const int32_t* positions, int T_, int heads, int kv_heads, int dim,
                      int block_size, int chunk, float scale, float softcap, const float* r1, const float* r2,
                      const void* gate, int ld_gate, float eps, void* out, int dtype, void* stream) {
+  return b200q_chunk_attn_seq(qs, cache, block_table, bt_stride, row_seq, positions, nullptr, 0, T_, heads, kv_heads, dim,
+                              block_size, chunk, scale, softcap, r1, r2, gate, ld_gate, eps, out, dtype, stream);
+}
+
+int b200q_chunk_attn_seq(const float* qs, const void* cache, const int32_t* block_table, int bt_stride,
+                         const int32_t* row_seq, const int32_t* positions, const int32_t* seq_desc, int n_seqs, int T_,
+                         int heads, int kv_heads, int dim, int block_size, int chunk, float scale, float softcap,
+                         const float* r1, const float* r2, const void* gate, int ld_gate, float eps, void* out,
+                         int dtype, void* stream) {
   B200Q_CHECK_ARG(qs && cache && block_table && row_seq && positions && r1 && r2 && gate && out && heads > 0 &&
                       kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && dim <= 512 && block_size > 0 && chunk >= 0 &&
                       T_ >= 0 && is_dtype(dtype),
                   "chunk_attn: bad argument (heads=%d kv_heads=%d dim=%d (<= 512))", heads, kv_heads, dim);
   if (T_ == 0) return B200Q_OK;
   const int rep = heads / kv_heads;
+  // bf16 caches with head sizes the tensor-core tiles take, when the caller gives the per-sequence view
+  if (seq_desc && n_seqs > 0 && dtype == B200Q_DTYPE_BF16 && (dim == 64 || dim == 128) && chunk_attn_mma_mode() &&
+      ((reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 && (ld_gate & 1) == 0 &&
+      (reinterpret_cast<uintptr_t>(gate) & 3) == 0) {
+    const int nw = rep < 8 ? rep : 8, parts = (rep + nw - 1) / nw;
+    const int ztiles = (T_ - n_seqs + 1 + 15) / 16;  // no portion of this step is longer than T - (n_seqs - 1)
+    dim3 mgrid(n_seqs, kv_heads * parts, ztiles);
+    B200Q_CHECK_ARG(mgrid.y <= 65535 && mgrid.z <= 65535, "chunk_attn: step too large (%d tokens)", T_);
+    const size_t msm = ((size_t)nw * 16 + 2 * CATT_KEYS) * (dim + 8) * 2 + 2 * CATT_KEYS * sizeof(float);
+#define MMA_ATTN(DD)                                                                                                 \
+  do {                                                                                                               \
+    if (msm > 48 * 1024)                                                                                             \
+      B200Q_CUDA(cudaFuncSetAttribute(chunk_attn_mma_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                      (int)msm));                                                                    \
+    chunk_attn_mma_kernel<DD><<<mgrid, nw * 32, msm, as_stream(stream)>>>(                                           \
+        qs, (const bf16*)cache, block_table, bt_stride, seq_desc, heads, kv_heads, block_size, chunk, scale, softcap, \
+        r1, r2, (const bf16*)gate, ld_gate, eps, (bf16*)out);                                                        \
+  } while (0)
+    if (dim == 64) MMA_ATTN(64);
+    else MMA_ATTN(128);
+#undef MMA_ATTN
+    B200Q_LAUNCH_CHECK();
+    return B200Q_OK;
+  }
   dim3 grid(T_, kv_heads, (rep + 7) / 8);
   const size_t smem = (size_t)(8 * dim + 32 * (dim + 1) + 32) * sizeof(float);
 #define ATTN(TT, ACC)                                                                                               \

@@ -162,6 +162,61 @@ def test_attention_edges_of_chunks_pages_and_tiles(cuda, dtype_name, chunk):
         assert float(diff.median()) > 0.05
 
 
+@pytest.mark.parametrize("D,H,G", [(64, 4, 1), (128, 8, 2), (64, 18, 2), (128, 3, 3)])
+@pytest.mark.parametrize("chunk", [50, 0])
+def test_attention_tensor_core_form_in_portions(cuda, D, H, G, chunk):
+    """the tile kernel (bf16 cache, head size 64 / 128), fed one sequence in portions of 1 to 150 tokens whose
+    16-token tiles straddle chunk edges, against the oracle; two sequences share a step at the end"""
+    L, lib = _ops()
+    T, bs = 310, 16
+    marks = sorted({3, 15, 16, 17, 63, 64, 65, 127, 128, 129, 255, 256} | ({e + d for e in range(chunk, T, chunk) for d in (-1, 0)} if chunk else set()))
+    qs, keys = _standout(T, H, G, D, [m for m in marks if m < T], 9)
+    r1, r2 = torch.linspace(0.2, 0.9, H), torch.linspace(0.1, 1.5, H)
+    kn = keys / torch.sqrt((keys * keys).mean(-1, keepdim=True) + 1e-6)
+    want = O.sink_attention(qs.double(), kn.double(), keys.double(), r1.double(), r2.double(), 0.2, 9.0, chunk)
+    nb = (T + bs - 1) // bs
+    pages = np.random.default_rng(1).permutation(2 * nb + 3)[:2 * nb].astype(np.int32).reshape(2, nb)
+    cache = torch.full(((2 * nb + 3) * bs, G * D), 1e4, dtype=torch.bfloat16, device=cuda)
+    for t in range(T):      # both sequences hold the same keys, in different pages
+        for q in range(2):
+            cache[int(pages[q, t // bs]) * bs + t % bs] = keys[t].reshape(-1).bfloat16()
+    bt = torch.tensor(pages, device=cuda).contiguous()
+    r1d, r2d = r1.to(cuda), r2.to(cuda)
+    got = torch.zeros(2, T, H * D)
+
+    def run(parts):   # parts: [(sequence, first position, tokens)]
+        rows = sum(n for _, _, n in parts)
+        q = torch.cat([qs[p0:p0 + n] for _, p0, n in parts]).to(cuda).float().contiguous()
+        desc, rseq, pos, at = [], [], [], 0
+        for k, (sq, p0, n) in enumerate(parts):
+            desc.append([at, n, p0, k])
+            rseq += [k] * n
+            pos += list(range(p0, p0 + n))
+            at += n
+        btab = torch.stack([bt[sq] for sq, _, _ in parts]).contiguous()
+        dd = torch.tensor(desc, dtype=torch.int32, device=cuda)
+        rs, ps = torch.tensor(rseq, dtype=torch.int32, device=cuda), torch.tensor(pos, dtype=torch.int32, device=cuda)
+        gate = torch.full((rows, H * D), 30.0, dtype=torch.bfloat16, device=cuda)
+        out = torch.zeros(rows, H * D, dtype=torch.bfloat16, device=cuda)
+        L.check(lib.b200q_chunk_attn_seq(q.data_ptr(), cache.data_ptr(), btab.data_ptr(), nb, rs.data_ptr(), ps.data_ptr(),
+                                         dd.data_ptr(), len(parts), rows, H, G, D, bs, chunk, 0.2, 9.0, r1d.data_ptr(),
+                                         r2d.data_ptr(), gate.data_ptr(), H * D, 1e-6, out.data_ptr(), L.DTYPE_BF16, None))
+        torch.cuda.synchronize()
+        at = 0
+        for sq, p0, n in parts:
+            got[sq, p0:p0 + n] = out[at:at + n].float().cpu()
+            at += n
+
+    at = 0
+    for n in [1, 1, 2, 45, 17, 1, 150, 33]:          # sequence 0 alone: 250 tokens
+        run([(0, at, n)])
+        at += n
+    run([(1, 0, 201), (0, 250, 1)])                 # a long portion of sequence 1 beside one token of sequence 0
+    run([(0, 251, 59), (1, 201, 109)])
+    for sq in range(2):
+        assert rel_err(got[sq].numpy(), want.reshape(T, -1).numpy()) < 2e-2, sq
+
+
 def test_attention_sink_takes_the_weight_when_no_key_fits(cuda):
     """all keys point away from the query: the scores sit at minus the cap, the silent zero-score term holds
     nearly all of the weight and the output is nearly zero (without that term it would be a mean of keys)"""
