@@ -13,6 +13,8 @@
 // does not depend on how its prompt was cut into steps, on its batch-mates, or on pages and slots.
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include "layered_common.cuh"
 
 namespace b200q {
@@ -449,6 +451,26 @@ __global__ void __launch_bounds__(256) chunk_attn_kernel(const float* __restrict
 // first token.
 // ------------------------------------------------------------------------------------------------
 constexpr int CATT_KEYS = 64;
+// The tensor-core kernels serve the bf16 model only: their softmax weights are rounded to bf16 (2^-9), so the
+// hardware exponential / logarithm (about 2^-21 relative) replace the full-precision library routines, which
+// were the larger part of the instruction stream.  tanh(x) = 1 - 2 / (e^2x + 1), exact in both limits.
+__device__ __forceinline__ float fast_tanh(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+// 1/rms of a cached key row of D bf16 values (one thread, 16-byte shared-memory loads, fixed order)
+template <int D>
+__device__ __forceinline__ float key_inv_rms(const bf16* row, float eps) {
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int c = 0; c < D / 8; ++c) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + c * 8);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      s0 = fmaf(bf16_lo(w[e]), bf16_lo(w[e]), s0);
+      s1 = fmaf(bf16_hi(w[e]), bf16_hi(w[e]), s1);
+    }
+  }
+  return rsqrtf((s0 + s1) / (float)D + eps);
+}
 template <int D>
 __global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __restrict__ qs, const bf16* __restrict__ cache,
                                                              const int32_t* __restrict__ block_table, int bt_stride,
@@ -456,7 +478,8 @@ __global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __rest
                                                              int kv_heads, int block_size, int chunk, float scale,
                                                              float softcap, const float* __restrict__ r1,
                                                              const float* __restrict__ r2, const bf16* __restrict__ gate,
-                                                             int ld_gate, float eps, bf16* __restrict__ out) {
+                                                             int ld_gate, float eps, bf16* __restrict__ out,
+                                                             int skip_single) {
   constexpr int LDS = D + 8;  // padded row (bf16 elements): ldmatrix rows fall on different banks
   extern __shared__ __align__(16) uint8_t smraw[];
   const int nw = blockDim.x >> 5;
@@ -465,7 +488,7 @@ __global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __rest
   float* kinv = reinterpret_cast<float*>(kbuf + 2 * CATT_KEYS * LDS);  // [2][64]
   const SeqView sq = seq_view(seq_desc, blockIdx.x);
   const int r0 = blockIdx.z * 16;
-  if (r0 >= sq.n) return;
+  if (r0 >= sq.n || (skip_single && sq.n == 1)) return;  // single tokens: the decode kernel's
   const int nrows = min(16, sq.n - r0);
   const int rep = heads / kv_heads, parts = (rep + nw - 1) / nw;
   const int g = blockIdx.y / parts, part = blockIdx.y % parts;
@@ -507,7 +530,7 @@ __global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __rest
   const uint32_t q_s = smem_u32(qsm + (long long)warp * 16 * LDS);
   const uint32_t a_off = (uint32_t)(((lane & 15) * LDS + (lane >> 4) * 8) * 2);
   const uint32_t kq_off = (uint32_t)((((lane & 7) + 8 * (lane >> 4)) * LDS + 8 * ((lane >> 3) & 1)) * 2);
-  const float c1 = r1[h], c2 = r2[h];
+  const float c1 = r1[h], c2 = r2[h], inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   // rows gq and gq + 8 of the tile belong to this thread
   int p_row[2], lo_row[2];
 #pragma unroll
@@ -528,16 +551,7 @@ __global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __rest
     if (c + 1 < ntiles) load_tile(c + 1, buf ^ 1);
     const bf16* kb = kbuf + (long long)buf * CATT_KEYS * LDS;
     float* kiv = kinv + buf * CATT_KEYS;
-    for (int j = warp; j < CATT_KEYS; j += nw) {  // 1/rms of every key of the tile, fixed order
-      float ss = 0.f;
-#pragma unroll
-      for (int d = lane; d < D; d += 32) {
-        const float v = __bfloat162float(kb[j * LDS + d]);
-        ss = fmaf(v, v, ss);
-      }
-      ss = warp_sum(ss);
-      if (lane == 0) kiv[j] = 1.f / sqrtf(ss / (float)D + eps);
-    }
+    for (int j = tid; j < CATT_KEYS; j += blockDim.x) kiv[j] = key_inv_rms<D>(kb + j * LDS, eps);  // thread per key
     __syncthreads();
     if (!live) continue;
     const uint32_t kb_s = smem_u32(kb);
@@ -566,8 +580,8 @@ __global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __rest
         float v = -INFINITY;
         if (j <= p_row[r] && j >= lo_row[r]) {
           v = s[nt][e] * kiv[kk] * scale;
-          if (softcap > 0.f) v = softcap * tanhf(v / softcap);
-          v -= c1 * log1pf(c2 * (float)(p_row[r] - j));
+          if (softcap > 0.f) v = softcap * fast_tanh(v * inv_cap);
+          v -= c1 * __logf(fmaf(c2, (float)(p_row[r] - j), 1.f));
         }
         s[nt][e] = v;
         rmax[r] = fmaxf(rmax[r], v);
@@ -578,7 +592,7 @@ __global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __rest
       rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 1));
       rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 2));
       const float mn = fmaxf(m_[r], rmax[r]);
-      corr[r] = expf(m_[r] - mn);
+      corr[r] = __expf(m_[r] - mn);
       m_[r] = mn;
     }
     float psum[2] = {0.f, 0.f};
@@ -586,7 +600,7 @@ __global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __rest
     for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float pv = round_bf16(expf(s[nt][e] - m_[e >> 1]));  // masked: exp(-inf) = 0
+        const float pv = round_bf16(__expf(s[nt][e] - m_[e >> 1]));  // masked: exp(-inf) = 0
         s[nt][e] = pv;
         psum[e >> 1] += pv;
       }
@@ -636,6 +650,210 @@ __global__ void __launch_bounds__(256) chunk_attn_mma_kernel(const float* __rest
       const float g0 = sigmoidf_(__bfloat162float(gr[d])), g1 = sigmoidf_(__bfloat162float(gr[d + 1]));
       *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16x2(o[nt][2 * r] * inv * g0, o[nt][2 * r + 1] * inv * g1);
     }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same for a single decoded token of a sequence: one CTA (4 warps) per (sequence, key/value head).  The M
+// rows of the tiles are the query heads of the group (<= 16), so one pass over the cached keys serves all of
+// them; warp w takes the 32-key tiles w, w+4, ... of the token's chunk through its own double-buffered
+// cp.async ring (no CTA barrier inside the loop) and keeps its own softmax state; the four states are merged
+// through shared memory in a fixed order at the end.  The sink is counted by warp 0.
+// ------------------------------------------------------------------------------------------------
+constexpr int CDEC_KEYS = 32, CDEC_WARPS = 4;
+template <int D>
+__global__ void __launch_bounds__(128) chunk_attn_decode_mma_kernel(const float* __restrict__ qs,
+                                                                    const bf16* __restrict__ cache,
+                                                                    const int32_t* __restrict__ block_table,
+                                                                    int bt_stride, const int32_t* __restrict__ seq_desc,
+                                                                    int heads, int kv_heads, int block_size, int chunk,
+                                                                    float scale, float softcap,
+                                                                    const float* __restrict__ r1,
+                                                                    const float* __restrict__ r2,
+                                                                    const bf16* __restrict__ gate, int ld_gate, float eps,
+                                                                    bf16* __restrict__ out) {
+  constexpr int LDS = D + 8;
+  extern __shared__ __align__(16) uint8_t smraw[];
+  bf16* qsm = reinterpret_cast<bf16*>(smraw);                              // [16][LDS]
+  bf16* kbuf = qsm + 16 * LDS;                                             // [4 warps][2][32][LDS]
+  float* kinv = reinterpret_cast<float*>(kbuf + CDEC_WARPS * 2 * CDEC_KEYS * LDS);  // [4][32]
+  float* mrg = reinterpret_cast<float*>(kbuf);                             // after the loop: [4][16][D + 2]
+  const SeqView sq = seq_view(seq_desc, blockIdx.x);
+  if (sq.n != 1) return;  // portions of prompts take the tile kernel
+  const int g = blockIdx.y, rep = heads / kv_heads;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q4 = lane & 3;
+  const int p = sq.pos0, lo = chunk > 0 ? p - p % chunk : 0;
+  const long long t = sq.row0;
+  const int32_t* bt = block_table + (long long)blockIdx.x * bt_stride;
+  const int GD = kv_heads * D;
+  const int ntiles = (p - lo) / CDEC_KEYS + 1;
+  bf16* kw = kbuf + (long long)warp * 2 * CDEC_KEYS * LDS;
+  float* kiv = kinv + warp * CDEC_KEYS;
+
+  auto load_tile = [&](int c, int buf) {  // by this warp alone
+    const int j0 = lo + c * CDEC_KEYS;
+    bf16* kb = kw + (long long)buf * CDEC_KEYS * LDS;
+    constexpr int CPR = D / 8;
+    for (int e = lane; e < CDEC_KEYS * CPR; e += 32) {
+      const int j = e / CPR, ck = e % CPR, pos = j0 + j;
+      bf16* dst = kb + j * LDS + ck * 8;
+      if (pos <= p) {
+        const long long row = (long long)bt[pos / block_size] * block_size + pos % block_size;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
+                     "l"(cache + row * GD + (long long)g * D + ck * 8)
+                     : "memory");
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (warp < ntiles) load_tile(warp, 0);
+  for (int e = tid; e < 16 * D; e += blockDim.x) {
+    const int r = e / D, d = e % D;
+    qsm[r * LDS + d] = __float2bfloat16_rn(r < rep ? qs[(t * heads + g * rep + r) * D + d] : 0.f);
+  }
+  __syncthreads();
+  const uint32_t q_s = smem_u32(qsm);
+  const uint32_t a_off = (uint32_t)(((lane & 15) * LDS + (lane >> 4) * 8) * 2);
+  const uint32_t kq_off = (uint32_t)((((lane & 7) + 8 * (lane >> 4)) * LDS + 8 * ((lane >> 3) & 1)) * 2);
+  float c1[2], c2[2];
+  bool row_on[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int hr = gq + 8 * r;
+    row_on[r] = hr < rep;
+    c1[r] = row_on[r] ? r1[g * rep + hr] : 0.f;
+    c2[r] = row_on[r] ? r2[g * rep + hr] : 0.f;
+  }
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const float l0 = (warp == 0 && q4 == 0) ? 1.f : 0.f;  // the sink, counted once per row
+  float m_[2] = {0.f, 0.f}, l_[2] = {l0, l0};
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int c = warp, it = 0; c < ntiles; c += CDEC_WARPS, ++it) {
+    const int buf = it & 1, j0 = lo + c * CDEC_KEYS;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    if (c + CDEC_WARPS < ntiles) load_tile(c + CDEC_WARPS, buf ^ 1);
+    const bf16* kb = kw + (long long)buf * CDEC_KEYS * LDS;
+    kiv[lane] = key_inv_rms<D>(kb + lane * LDS, eps);  // lane per key
+    __syncwarp();
+    const uint32_t kb_s = smem_u32(kb);
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldsm_x4(q_s + a_off + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+      for (int nt2 = 0; nt2 < 2; ++nt2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(kb_s + kq_off + (uint32_t)(nt2 * 16 * LDS * 2 + ks * 32), b0, b1, b2, b3);
+        mma_bf16_16816(s[2 * nt2], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(s[2 * nt2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    float rmax[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kk = nt * 8 + 2 * q4 + (e & 1), j = j0 + kk, r = e >> 1;
+        float v = -INFINITY;
+        if (row_on[r] && j <= p) {
+          v = s[nt][e] * kiv[kk] * scale;
+          if (softcap > 0.f) v = softcap * fast_tanh(v * inv_cap);
+          v -= c1[r] * __logf(fmaf(c2[r], (float)(p - j), 1.f));
+        }
+        s[nt][e] = v;
+        rmax[r] = fmaxf(rmax[r], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 1));
+      rmax[r] = fmaxf(rmax[r], __shfl_xor_sync(0xffffffffu, rmax[r], 2));
+      const float mn = fmaxf(m_[r], rmax[r]);
+      corr[r] = __expf(m_[r] - mn);
+      m_[r] = mn;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = round_bf16(__expf(s[nt][e] - m_[e >> 1]));
+        s[nt][e] = pv;
+        psum[e >> 1] += pv;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) l_[r] = l_[r] * corr[r] + psum[r];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk2 = 0; kk2 < CDEC_KEYS / 16; ++kk2) {
+      const uint32_t a0 = pack_bf16x2(s[2 * kk2][0], s[2 * kk2][1]), a1 = pack_bf16x2(s[2 * kk2][2], s[2 * kk2][3]);
+      const uint32_t a2 = pack_bf16x2(s[2 * kk2 + 1][0], s[2 * kk2 + 1][1]),
+                     a3 = pack_bf16x2(s[2 * kk2 + 1][2], s[2 * kk2 + 1][3]);
+      const int key = kk2 * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const uint32_t v_row = kb_s + (uint32_t)((key * LDS + 8 * (lane >> 4)) * 2);
+#pragma unroll
+      for (int nd2 = 0; nd2 < D / 16; ++nd2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(v_row + nd2 * 32, b0, b1, b2, b3);
+        mma_bf16_16816(o[2 * nd2], a0, a1, a2, a3, b0, b1);
+        mma_bf16_16816(o[2 * nd2 + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+  }
+  // ---- merge the four warps' states: [warp][row][D + 2] = (o..., m, l) ----
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_[r] += __shfl_xor_sync(0xffffffffu, l_[r], 1);
+    l_[r] += __shfl_xor_sync(0xffffffffu, l_[r], 2);
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();  // every warp is done with its key buffers: they become the merge area
+  constexpr int MS = D + 2;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float* dst = mrg + ((long long)warp * 16 + gq + 8 * r) * MS;
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+      dst[nt * 8 + 2 * q4] = o[nt][2 * r];
+      dst[nt * 8 + 2 * q4 + 1] = o[nt][2 * r + 1];
+    }
+    if (q4 == 0) {
+      dst[D] = m_[r];
+      dst[D + 1] = l_[r];
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < rep * D; e += blockDim.x) {
+    const int r = e / D, d = e % D;
+    float mx = 0.f;
+#pragma unroll
+    for (int w = 0; w < CDEC_WARPS; ++w) mx = fmaxf(mx, mrg[((long long)w * 16 + r) * MS + D]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < CDEC_WARPS; ++w) {
+      const float* src = mrg + ((long long)w * 16 + r) * MS;
+      const float f = expf(src[D] - mx);
+      num = fmaf(src[d], f, num);
+      den = fmaf(src[D + 1], f, den);
+    }
+    const int h = g * rep + r;
+    const float gv = sigmoidf_(__bfloat162float(gate[t * ld_gate + (long long)h * D + d]));
+    out[(t * heads + h) * D + d] = __float2bfloat16_rn(num / den * gv);
   }
 }
 
@@ -886,19 +1104,37 @@ int b200q_chunk_attn_seq(const float* qs, const void* cache, const int32_t* bloc
     dim3 mgrid(n_seqs, kv_heads * parts, ztiles);
     B200Q_CHECK_ARG(mgrid.y <= 65535 && mgrid.z <= 65535, "chunk_attn: step too large (%d tokens)", T_);
     const size_t msm = ((size_t)nw * 16 + 2 * CATT_KEYS) * (dim + 8) * 2 + 2 * CATT_KEYS * sizeof(float);
+    // single decoded tokens go to the kernel whose rows are the heads of a group (groups of up to 16 heads);
+    // a step of single tokens only (T == n_seqs) needs no tile kernel, and the other way round is not known
+    // here, so the decode kernel is launched whenever it can serve (sequences with portions leave it at once)
+    const bool dec = rep <= 16, tiles = !dec || T_ > n_seqs;
+    const size_t dsm = std::max((size_t)(16 + CDEC_WARPS * 2 * CDEC_KEYS) * (dim + 8) * 2 + CDEC_WARPS * CDEC_KEYS * 4,
+                                (size_t)16 * (dim + 8) * 2 + (size_t)CDEC_WARPS * 16 * (dim + 2) * 4);
+    dim3 dgrid(n_seqs, kv_heads);
 #define MMA_ATTN(DD)                                                                                                 \
   do {                                                                                                               \
-    if (msm > 48 * 1024)                                                                                             \
-      B200Q_CUDA(cudaFuncSetAttribute(chunk_attn_mma_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
-                                      (int)msm));                                                                    \
-    chunk_attn_mma_kernel<DD><<<mgrid, nw * 32, msm, as_stream(stream)>>>(                                           \
-        qs, (const bf16*)cache, block_table, bt_stride, seq_desc, heads, kv_heads, block_size, chunk, scale, softcap, \
-        r1, r2, (const bf16*)gate, ld_gate, eps, (bf16*)out);                                                        \
+    if (tiles) {                                                                                                     \
+      if (msm > 48 * 1024)                                                                                           \
+        B200Q_CUDA(cudaFuncSetAttribute(chunk_attn_mma_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                        (int)msm));                                                                  \
+      chunk_attn_mma_kernel<DD><<<mgrid, nw * 32, msm, as_stream(stream)>>>(                                         \
+          qs, (const bf16*)cache, block_table, bt_stride, seq_desc, heads, kv_heads, block_size, chunk, scale,       \
+          softcap, r1, r2, (const bf16*)gate, ld_gate, eps, (bf16*)out, dec ? 1 : 0);                                \
+      B200Q_LAUNCH_CHECK();                                                                                          \
+    }                                                                                                                \
+    if (dec) {                                                                                                       \
+      if (dsm > 48 * 1024)                                                                                           \
+        B200Q_CUDA(cudaFuncSetAttribute(chunk_attn_decode_mma_kernel<DD>,                                            \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm));                     \
+      chunk_attn_decode_mma_kernel<DD><<<dgrid, 128, dsm, as_stream(stream)>>>(                                      \
+          qs, (const bf16*)cache, block_table, bt_stride, seq_desc, heads, kv_heads, block_size, chunk, scale,       \
+          softcap, r1, r2, (const bf16*)gate, ld_gate, eps, (bf16*)out);                                             \
+      B200Q_LAUNCH_CHECK();                                                                                          \
+    }                                                                                                                \
   } while (0)
     if (dim == 64) MMA_ATTN(64);
     else MMA_ATTN(128);
 #undef MMA_ATTN
-    B200Q_LAUNCH_CHECK();
     return B200Q_OK;
   }
   dim3 grid(T_, kv_heads, (rep + 7) / 8);
