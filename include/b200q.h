@@ -526,7 +526,19 @@ int b200q_model_create(const b200q_model_config* cfg, b200q_model_t* out);
  *   PolyNorm ff: "mlp.up" [ff, W], "mlp.act" [1, 4], "mlp.down" [W, ff]
  *   MoE ff: "mlp.router" [E, W], "mlp.router_bias" [1, E], "mlp.experts_gate_up" [E*2*ff, W] (per expert:
  *     gate rows then up rows), "mlp.experts_down" [E*W, ff], and with a shared expert
- *     "mlp.shared_gate_up" [2*ffs, W], "mlp.shared_down" [W, ffs], "mlp.shared_gate" [1, W] */
+ *     "mlp.shared_gate_up" [2*ffs, W], "mlp.shared_down" [W, ffs], "mlp.shared_gate" [1, W]
+ * B200Q_ARCH_NORIDRA (cfg.layer_form = B200Q_FORM_POSTNORM, with norm_groups, residual_alpha, input_taps,
+ * learned_pos): "pos" [>= max_pos, W] beside "embed"; per layer "norm1", "ls1" [1, W] (and "norm2", "ls2" with a
+ * feed-forward), "canon1" / "canon2" [1, W*input_taps] (fp32 tap table [W][taps], last tap = current token), and
+ *   gated delta: "mix.proj" [2*kv_heads*dim + 2*heads*vdim, W] (rows: q, k, v, gate), "mix.ba" [2*heads, W] (rows:
+ *     beta, decay input), "mix.conv" [1, (2*kv_heads*dim + heads*vdim)*conv_taps] (taps of the channels q | k | v),
+ *     "mix.a_log", "mix.dt_bias" [1, heads], "mix.out_norm" [1, vdim], "mix.o" [W, heads*vdim]
+ *   chunk attention: "mix.proj" [(2*heads + kv_heads)*dim, W] (rows: q, k, gate), "mix.q_norm", "mix.k_norm"
+ *     [1, dim], "mix.r1", "mix.r2" [1, heads], "mix.o" [W, heads*dim]
+ *   selective scan: "mix.proj" [2*inner, W] (rows: x, z), "mix.conv" [1, inner*conv_taps], "mix.conv_b" [1, inner],
+ *     "mix.x" [roundup64(dt_rank + 2*state_dim), inner] (rows: dt, B, C, then zero rows), "mix.dt" [inner, dt_rank],
+ *     "mix.dt_b" [1, inner], "mix.a_log" [1, inner*state_dim], "mix.d" [1, inner], "mix.o" [W, inner]
+ *   sigmoid-routed experts: "mlp.router" [E, W], "mlp.experts_gate_up" [E*2*ff, W], "mlp.experts_down" [E*W, ff] */
 int b200q_model_create_layered(const b200q_model_config* cfg, const b200q_layer_desc* layers,
                                b200q_model_t* out);
 /* layered models: bytes of one cache block over all layers that own a latent cache (the caller allocates
