@@ -146,21 +146,22 @@ __global__ void __launch_bounds__(256) linear_kernel(LinearArgs a) {
   }
 }
 
-// few outputs per row (a router, a gate): one warp per (row, 8 outputs), lanes stride over K — every SM
-// gets work even when the whole product has a handful of 64 x 64 tiles.  Lane partials are summed in a
-// fixed order, so a row's result does not depend on the batch.
-template <typename T, typename TC>
+// few outputs per row (a router, a gate): one warp per (row, OPW outputs), lanes stride over K — every SM
+// gets work even when the whole product has a handful of 64 x 64 tiles (OPW = 8, or 2 when even that leaves
+// most SMs without a warp: decode-sized batches).  Lane partials are summed in a fixed order that does not
+// depend on OPW, so a row's result does not depend on the batch.
+template <typename T, typename TC, int OPW>
 __global__ void __launch_bounds__(256) skinny_linear_kernel(LinearArgs a) {
   const long long wg = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31, n_groups = (a.N + 7) / 8;
+  const int lane = threadIdx.x & 31, n_groups = (a.N + OPW - 1) / OPW;
   const long long m = wg / n_groups;
-  const int n0 = (int)(wg % n_groups) * 8;
+  const int n0 = (int)(wg % n_groups) * OPW;
   if (m >= a.M) return;
   const T* A = (const T*)a.A + m * a.lda;
   const T* Wm = (const T*)a.W;
-  float acc[8];
+  float acc[OPW];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  for (int j = 0; j < OPW; ++j) acc[j] = 0.f;
   bool vec_done = false;
   if constexpr (sizeof(T) == 2) {
     // bf16 rows whose start is 16-byte aligned: 8 elements per load
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(256) skinny_linear_kernel(LinearArgs a) {
         const uint4 av = ld_v4(A + k);
         const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < OPW; ++j)
           if (n0 + j < a.N) {
             const uint4 wv = ld_nc_v4(Wm + (long long)(n0 + j) * a.K + k);
             const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -187,11 +188,11 @@ __global__ void __launch_bounds__(256) skinny_linear_kernel(LinearArgs a) {
     for (int k = lane; k < a.K; k += 32) {
       const float av = ldf(A + k);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
+      for (int j = 0; j < OPW; ++j)
         if (n0 + j < a.N) acc[j] = fmaf(av, ldf(Wm + (long long)(n0 + j) * a.K + k), acc[j]);
     }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < OPW; ++j) {
     const float v = warp_sum(acc[j]);
     if (lane == 0 && n0 + j < a.N) stf((TC*)a.C + m * a.ldc + n0 + j, v + (a.bias ? a.bias[n0 + j] : 0.f));
   }
@@ -1272,11 +1273,20 @@ int b200q_centered_rmsnorm(const float* x, const int32_t* rows, const float* w1,
 static int launch_linear(const LinearArgs& a, int tiles_m, int nz, int dtype, int out_f32, void* stream) {
   if (tiles_m <= 0 || nz <= 0 || a.N <= 0) return B200Q_OK;
   if (nz == 1 && !a.group_off && a.N <= 64) {
-    const long long warps = (long long)a.M * ((a.N + 7) / 8);
+    // fewer outputs per warp when 8 would leave most of the 148 SMs without a warp
+    const bool narrow = (long long)a.M * ((a.N + 7) / 8) < 148 * 16;
+    const int opw = narrow ? 2 : 8;
+    const long long warps = (long long)a.M * ((a.N + opw - 1) / opw);
     const unsigned blocks = (unsigned)((warps + 7) / 8);
-    if (dtype == B200Q_DTYPE_F32) skinny_linear_kernel<float, float><<<blocks, 256, 0, as_stream(stream)>>>(a);
-    else if (out_f32) skinny_linear_kernel<bf16, float><<<blocks, 256, 0, as_stream(stream)>>>(a);
-    else skinny_linear_kernel<bf16, bf16><<<blocks, 256, 0, as_stream(stream)>>>(a);
+#define SKINNY(TT, TC)                                                                     \
+  do {                                                                                     \
+    if (narrow) skinny_linear_kernel<TT, TC, 2><<<blocks, 256, 0, as_stream(stream)>>>(a); \
+    else skinny_linear_kernel<TT, TC, 8><<<blocks, 256, 0, as_stream(stream)>>>(a);        \
+  } while (0)
+    if (dtype == B200Q_DTYPE_F32) SKINNY(float, float);
+    else if (out_f32) SKINNY(bf16, float);
+    else SKINNY(bf16, bf16);
+#undef SKINNY
     B200Q_LAUNCH_CHECK();
     return B200Q_OK;
   }
