@@ -4,7 +4,7 @@
 // contiguous "page" of BS*D*2 bytes per (block, K|V, kv-head).  Inside a token row the 16-byte
 // chunk c lives at chunk position c ^ (token_in_block & 7).  The swizzle is applied by the
 // RoPE+KV-write kernel (elementwise.cu), so a page can be pulled into shared memory with ONE
-// 1-D TMA bulk copy (cp.async.bulk, SASS UBLKCP) of exactly the valid rows and then be read
+// 1-D TMA bulk copy (cp.async.bulk) of exactly the valid rows and then be read
 // with ldmatrix without bank conflicts — the block-table gather is done by the TMA engine, no
 // thread touches KV bytes in flight.
 //

@@ -120,7 +120,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // ---- TMA -------------------------------------------------------------------------------------
-// 1-D bulk copy global -> shared, completion on an mbarrier (SASS: UBLKCP)
+// 1-D bulk copy global -> shared, completion on an mbarrier
 __device__ __forceinline__ void tma_bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes,
                                              uint64_t* bar) {
   asm volatile(
@@ -128,7 +128,7 @@ __device__ __forceinline__ void tma_bulk_g2s(void* smem_dst, const void* gsrc, u
       ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
-// 2-D tiled tensor-map load (SASS: UTMALDG)
+// 2-D tiled tensor-map load
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int c0, int c1,
                                             uint64_t* bar) {
   asm volatile(
