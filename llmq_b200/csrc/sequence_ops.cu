@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(256) conv_state_kernel(const TI* __restrict__ 
 // gated delta rule, three launches.
 //   prepare (CTA per token): q, k -> unit vectors per head (q also times dim^-1/2), in place in the fp32
 //           qkv rows; ba row (beta logits | decay inputs) -> (beta | g) in place
-//   recur   (one warp per sequence x head x 32 value columns, lane j = column j, S[0..dim) in registers):
+//   recur   (one warp per sequence x head x 8 value columns, 4 lanes per column, a quarter of S[0..dim) each):
 //           S <- g S;  u = beta (v_j - k.S);  S <- S + k u;  o_j = q.S   -> raw [T, heads*vdim] (fp32)
 //   finish  (CTA per token x head): out = raw / rms(raw) * out_norm * silu(gate)
 // ------------------------------------------------------------------------------------------------
@@ -190,11 +190,13 @@ __global__ void __launch_bounds__(128) gdelta_prepare_kernel(float* __restrict__
   }
 }
 
-// One warp per (sequence, head, 32 value columns): columns are independent, so a head's state is spread over
-// vdim/32 CTAs.  Lane j keeps column j of the state (dim values, zero-padded to DT) in registers; k and q of 8
-// tokens at a time arrive in shared memory by cp.async one group ahead of the one being consumed, v of the
-// group is prefetched into registers, and both dot products run as four independent FMA chains.
-constexpr int GDELTA_G = 8;
+// One warp per (sequence, head, 8 value columns): columns are independent, so a head's state is spread over
+// vdim/8 CTAs, and inside the warp every column is shared by 4 lanes that each keep a quarter of the column
+// (dim/4 values, zero-padded) in registers and sum their partial dot products by two butterfly shuffles — a
+// single warp is bound by its own instruction stream, and there are far more SMs than (sequence, head) pairs
+// in a prompt step.  k and q of 8 tokens at a time arrive in shared memory by cp.async one group ahead of the
+// one being consumed, v of the group is prefetched into registers.
+constexpr int GDELTA_G = 8, GDELTA_COLS = 8;
 __device__ __forceinline__ void cp_async16_(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
@@ -203,9 +205,11 @@ __global__ void __launch_bounds__(32) gdelta_recur_kernel(const float* __restric
                                                           float* __restrict__ state, long long slot_stride,
                                                           const int32_t* __restrict__ seq_desc, int heads, int kv_heads,
                                                           int dim, int vdim, float* __restrict__ raw) {
+  constexpr int QL = DT / 4;  // state values per lane
   extern __shared__ __align__(16) float sm[];  // [2][G][2*DT]: k (padded to DT) then q (padded to DT)
   const SeqView s = seq_view(seq_desc, blockIdx.x);
-  const int h = blockIdx.y, lane = threadIdx.x, j = blockIdx.z * 32 + lane, kvh = h / (heads / kv_heads);
+  const int h = blockIdx.y, lane = threadIdx.x, sub = lane >> 3, j = blockIdx.z * GDELTA_COLS + (lane & 7);
+  const int kvh = h / (heads / kv_heads), q0 = sub * QL;
   const int GD = kv_heads * dim, ldq = 2 * GD + heads * vdim, HV = heads * vdim;
   const bool on = j < vdim;
   // 16-byte copies need every k and q vector to start on a 16-byte boundary: head size, row stride and base
@@ -235,9 +239,9 @@ __global__ void __launch_bounds__(32) gdelta_recur_kernel(const float* __restric
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   fetch(0, 0);
-  float S[DT];
+  float S[QL];
 #pragma unroll
-  for (int q = 0; q < DT; ++q) S[q] = (on && q < dim && s.pos0 > 0) ? st[(long long)q * vdim + j] : 0.f;
+  for (int q = 0; q < QL; ++q) S[q] = (on && q0 + q < dim && s.pos0 > 0) ? st[(long long)(q0 + q) * vdim + j] : 0.f;
   for (int g0 = 0, buf = 0; g0 < s.n; g0 += GDELTA_G, buf ^= 1) {
     const int cnt = min(GDELTA_G, s.n - g0);
     float vj[GDELTA_G];
@@ -254,16 +258,16 @@ __global__ void __launch_bounds__(32) gdelta_recur_kernel(const float* __restric
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();  // this group has landed; the other buffer is no longer read
     if (g0 + GDELTA_G < s.n) fetch(g0 + GDELTA_G, buf ^ 1);
-    const float* base = sm + (long long)buf * GDELTA_G * 2 * DT;
+    const float* base = sm + (long long)buf * GDELTA_G * 2 * DT + q0;
 #pragma unroll
     for (int tk = 0; tk < GDELTA_G; ++tk) {
       if (tk < cnt) {
         const float beta = __shfl_sync(0xffffffffu, my_b, tk), g = __shfl_sync(0xffffffffu, my_g, tk);
         const float4* k4 = reinterpret_cast<const float4*>(base + tk * 2 * DT);
-        const float4* q4 = k4 + DT / 4;
+        const float4* q4 = reinterpret_cast<const float4*>(base + tk * 2 * DT + DT);
         float u0 = 0.f, u1 = 0.f, u2 = 0.f, u3 = 0.f;
 #pragma unroll
-        for (int q = 0; q < DT / 4; ++q) {
+        for (int q = 0; q < QL / 4; ++q) {
           const float4 k = k4[q];
           S[4 * q] *= g;
           S[4 * q + 1] *= g;
@@ -274,10 +278,13 @@ __global__ void __launch_bounds__(32) gdelta_recur_kernel(const float* __restric
           u2 = fmaf(k.z, S[4 * q + 2], u2);
           u3 = fmaf(k.w, S[4 * q + 3], u3);
         }
-        const float u = beta * (vj[tk] - ((u0 + u1) + (u2 + u3)));
+        float kS = (u0 + u1) + (u2 + u3);  // this lane's quarter; the column's sum over its four lanes
+        kS += __shfl_xor_sync(0xffffffffu, kS, 8);
+        kS += __shfl_xor_sync(0xffffffffu, kS, 16);
+        const float u = beta * (vj[tk] - kS);
         float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-        for (int q = 0; q < DT / 4; ++q) {
+        for (int q = 0; q < QL / 4; ++q) {
           const float4 k = k4[q], qq = q4[q];
           S[4 * q] = fmaf(k.x, u, S[4 * q]);
           S[4 * q + 1] = fmaf(k.y, u, S[4 * q + 1]);
@@ -288,14 +295,17 @@ __global__ void __launch_bounds__(32) gdelta_recur_kernel(const float* __restric
           o2 = fmaf(S[4 * q + 2], qq.z, o2);
           o3 = fmaf(S[4 * q + 3], qq.w, o3);
         }
-        if (on) raw[(long long)(s.row0 + g0 + tk) * HV + h * vdim + j] = (o0 + o1) + (o2 + o3);
+        float o = (o0 + o1) + (o2 + o3);
+        o += __shfl_xor_sync(0xffffffffu, o, 8);
+        o += __shfl_xor_sync(0xffffffffu, o, 16);
+        if (on && sub == 0) raw[(long long)(s.row0 + g0 + tk) * HV + h * vdim + j] = o;
       }
     }
   }
   if (on) {
 #pragma unroll
-    for (int q = 0; q < DT; ++q)
-      if (q < dim) st[(long long)q * vdim + j] = S[q];
+    for (int q = 0; q < QL; ++q)
+      if (q0 + q < dim) st[(long long)(q0 + q) * vdim + j] = S[q];
   }
 }
 
@@ -894,6 +904,16 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
   const float dc = on ? dvec[c] : 0.f, dtb = (on && dt_bias) ? dt_bias[c] : 0.f;
   for (int g0 = 0; g0 < s.n; g0 += SCAN_G) {
     const int cnt = min(SCAN_G, s.n - g0);
+    // this channel's inputs of the whole group are fetched before the chain starts
+    float dtv[SCAN_G], xs[SCAN_G], zs[SCAN_G];
+#pragma unroll
+    for (int tk = 0; tk < SCAN_G; ++tk) {
+      const bool ok = on && tk < cnt;
+      const long long r = s.row0 + g0 + tk;
+      dtv[tk] = ok ? dt_raw[r * inner + c] : 0.f;
+      xs[tk] = ok ? ldf(x + r * inner + c) : 0.f;
+      zs[tk] = ok ? ldf(z + r * ld_z + c) : 0.f;
+    }
     __syncthreads();
     for (int e = threadIdx.x; e < cnt * 2 * N; e += blockDim.x) {
       const int tk = e / (2 * N), i = e % (2 * N);
@@ -901,20 +921,23 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
     }
     __syncthreads();
     if (!on) continue;
-    for (int tk = 0; tk < cnt; ++tk) {
-      const long long r = s.row0 + g0 + tk;
-      const float* Bv = sm + tk * 2 * N;
-      const float* Cv = Bv + N;
-      const float dt = softplusf_(dt_raw[r * inner + c] + dtb), xv = ldf(x + r * inner + c), dx = dt * xv;
-      float y = 0.f;
 #pragma unroll
-      for (int n = 0; n < NT; ++n)
-        if (n < N) {
-          S[n] = fmaf(decay_of<T>(dt * A[n]), S[n], dx * Bv[n]);
-          y = fmaf(S[n], Cv[n], y);
-        }
-      y = fmaf(dc, xv, y);
-      stf(out + r * inner + c, y * siluf_(ldf(z + r * ld_z + c)));
+    for (int tk = 0; tk < SCAN_G; ++tk) {
+      if (tk < cnt) {
+        const long long r = s.row0 + g0 + tk;
+        const float* Bv = sm + tk * 2 * N;
+        const float* Cv = Bv + N;
+        const float dt = softplusf_(dtv[tk] + dtb), xv = xs[tk], dx = dt * xv;
+        float y = 0.f;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+          if (n < N) {
+            S[n] = fmaf(decay_of<T>(dt * A[n]), S[n], dx * Bv[n]);
+            y = fmaf(S[n], Cv[n], y);
+          }
+        y = fmaf(dc, xv, y);
+        stf(out + r * inner + c, y * siluf_(zs[tk]));
+      }
     }
   }
   if (on) {
@@ -1035,7 +1058,8 @@ int b200q_gated_delta(float* qkv, float* ba, float* raw, const void* gate, int l
   gdelta_prepare_kernel<<<T_, 128, 0, st>>>(q, b, a_log, dt_bias, heads, kv_heads, dim, vdim);
   B200Q_LAUNCH_CHECK();
   const int threads = (vdim + 31) & ~31;
-  dim3 grid(n_seqs, heads, (vdim + 31) / 32);
+  dim3 grid(n_seqs, heads, (vdim + GDELTA_COLS - 1) / GDELTA_COLS);
+  B200Q_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "gated_delta: too many heads or value columns");
 #define RECUR(DT)                                                                                                  \
   do {                                                                                                             \
     const size_t smem = (size_t)2 * GDELTA_G * 2 * DT * sizeof(float);                                             \
