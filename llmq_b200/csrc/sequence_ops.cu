@@ -963,6 +963,26 @@ __global__ void __launch_bounds__(256) scatter_scaled_rows_kernel(const T* __res
     stf(dst + (long long)pair_pos[p] * W + c, ldf(src + (p / top) * W + c) * wts[p]);
   }
 }
+// bf16 rows of a multiple of 8 values, 16-byte aligned: 8 values per thread
+__global__ void __launch_bounds__(256) scatter_scaled_rows_v8_kernel(const bf16* __restrict__ src,
+                                                                     const int32_t* __restrict__ pair_pos,
+                                                                     const float* __restrict__ wts, int top,
+                                                                     bf16* __restrict__ dst, long long pairs, int W) {
+  const int per = W / 8;
+  const long long total = pairs * per;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long long)gridDim.x * blockDim.x) {
+    const long long p = e / per;
+    const int c = (int)(e % per) * 8;
+    const float w = wts[p];
+    const uint4 v = ld_v4(src + (p / top) * W + c);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = pack_bf16x2(bf16_lo(in[i]) * w, bf16_hi(in[i]) * w);
+    st_v4(dst + (long long)pair_pos[p] * W + c, make_uint4(o[0], o[1], o[2], o[3]));
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256) silu_glu_kernel(const T* __restrict__ gu, T* __restrict__ y, long long rows,
@@ -973,6 +993,23 @@ __global__ void __launch_bounds__(256) silu_glu_kernel(const T* __restrict__ gu,
     const long long r = e / F;
     const int c = (int)(e % F);
     stf(y + e, siluf_(ldf(gu + r * 2 * F + c)) * ldf(gu + r * 2 * F + F + c));
+  }
+}
+__global__ void __launch_bounds__(256) silu_glu_v8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ y,
+                                                          long long rows, int F) {
+  const int per = F / 8;
+  const long long total = rows * per;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long long)gridDim.x * blockDim.x) {
+    const long long r = e / per;
+    const int c = (int)(e % per) * 8;
+    const uint4 g = ld_v4(gu + r * 2 * F + c), u = ld_v4(gu + r * 2 * F + F + c);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      o[i] = pack_bf16x2(siluf_(bf16_lo(gw[i])) * bf16_lo(uw[i]), siluf_(bf16_hi(gw[i])) * bf16_hi(uw[i]));
+    st_v4(y + r * F + c, make_uint4(o[0], o[1], o[2], o[3]));
   }
 }
 
@@ -1224,6 +1261,13 @@ int b200q_scatter_scaled_rows(const void* src, const int32_t* pair_pos, const fl
                   "scatter_scaled_rows: bad argument");
   if (T_ == 0) return B200Q_OK;
   const long long pairs = (long long)T_ * top;
+  if (dtype == B200Q_DTYPE_BF16 && W % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+    scatter_scaled_rows_v8_kernel<<<grid_for(pairs * (W / 8)), 256, 0, as_stream(stream)>>>(
+        (const bf16*)src, pair_pos, wts, top, (bf16*)dst, pairs, W);
+    B200Q_LAUNCH_CHECK();
+    return B200Q_OK;
+  }
   DISPATCH_T(dtype, (scatter_scaled_rows_kernel<T><<<grid_for(pairs * W), 256, 0, as_stream(stream)>>>(
                         (const T*)src, pair_pos, wts, top, (T*)dst, pairs, W)));
   B200Q_LAUNCH_CHECK();
@@ -1233,6 +1277,12 @@ int b200q_scatter_scaled_rows(const void* src, const int32_t* pair_pos, const fl
 int b200q_silu_glu(const void* gate_up, void* y, int64_t rows, int F, int dtype, void* stream) {
   B200Q_CHECK_ARG(gate_up && y && rows >= 0 && F > 0 && is_dtype(dtype), "silu_glu: bad argument");
   if (rows == 0) return B200Q_OK;
+  if (dtype == B200Q_DTYPE_BF16 && F % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+    silu_glu_v8_kernel<<<grid_for(rows * (F / 8)), 256, 0, as_stream(stream)>>>((const bf16*)gate_up, (bf16*)y, rows, F);
+    B200Q_LAUNCH_CHECK();
+    return B200Q_OK;
+  }
   DISPATCH_T(dtype, (silu_glu_kernel<T><<<grid_for(rows * F), 256, 0, as_stream(stream)>>>((const T*)gate_up, (T*)y,
                                                                                          rows, F)));
   B200Q_LAUNCH_CHECK();
