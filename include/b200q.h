@@ -351,12 +351,13 @@ int b200q_chunk_attn_seq(const float* qs_dev, const void* cache_dev, const int32
  * softplus), dt_bias: fp32 [inner] added to it (NULL: none); bc: model dtype rows (ld_bc) whose entries [b_off, b_off + N) are B and
  * [b_off + N, b_off + 2N) are C; z: model dtype rows (ld_z); a_log: fp32 [inner, N]; d: fp32 [inner].
  *   dt = softplus(dt_raw + dt_bias);  S[c,n] <- exp(dt_c * -exp(a_log[c,n])) S[c,n] + dt_c x_c B_n;
- *   y_c = sum_n S[c,n] C_n + d_c x_c;  out = y * silu(z).     state: fp32 [inner][N] per slot. */
+ *   y_c = sum_n S[c,n] C_n + d_c x_c;  out = y * silu(z).     state: fp32 [N][inner] per slot.  T = rows of the
+ *   step (T > n_seqs: prompt portions are present and a channel's state is split over four lanes). */
 int b200q_selective_scan(const void* x_dev, const float* dt_raw_dev, const float* dt_bias_dev, const void* bc_dev,
                          int ld_bc, int b_off,
                          const void* z_dev, int ld_z, const float* a_log_dev, const float* d_dev, float* state_dev,
                          long long slot_stride, const int32_t* seq_desc_dev, int n_seqs, int inner, int N,
-                         void* out_dev, int dtype, void* stream);
+                         void* out_dev, int T, int dtype, void* stream);
 /* routed experts whose weight scales the INPUT: dst[pair_pos[p], :] = src[p / top, :] * wts[p] for every
  * (token, choice) pair p < T*top (rows land in expert order for the grouped linear) */
 int b200q_scatter_scaled_rows(const void* src_dev, const int32_t* pair_pos_dev, const float* wts_dev, int top,

@@ -572,7 +572,7 @@ int layered_forward(b200q_model* m, const b200q_batch* b, void* stream) {
       uint8_t* z = (uint8_t*)y->proj + (size_t)I * es;
       TRY(B200Q_PROF_PREFILL_ATTN, 8.0 * b->n_rows * (double)I * N,
           b200q_selective_scan(y->xc, y->dtr, l.dt_b, y->xp, NX, R, z, 2 * I, l.a_log, l.dvec, y->state + l.state_off,
-                               y->state_slot_floats, b->seq_desc, b->n_rows, I, N, y->attn, dt, stream));
+                               y->state_slot_floats, b->seq_desc, b->n_rows, I, N, y->attn, T, dt, stream));
       LIN(y->attn, I, l.o, nullptr, y->mix, W, W, I, 0);
     }
     return B200Q_OK;

@@ -868,17 +868,20 @@ __global__ void __launch_bounds__(128) chunk_attn_decode_mma_kernel(const float*
 }
 
 // ------------------------------------------------------------------------------------------------
-// selective scan: one CTA per (sequence, 128 channels), thread = channel, the channel's state S[0..N) and
-// its decay rates A[n] = -exp(a_log) in registers; B and C of 8 tokens at a time are staged in shared
-// memory (they are shared by all channels).  State layout in the slot: [N][inner] (coalesced over channels).
+// selective scan: one CTA per (sequence, 32 channels); four lanes share a channel, each with a quarter of its
+// state S[0..N) and of its decay rates A[n] = -exp(a_log) in registers, their partial outputs summed by two
+// butterfly shuffles (a prompt step has few sequences and a warp is bound by its own instruction stream, so
+// the channel's chain is cut in four).  B and C of 8 tokens at a time are staged in shared memory (they are
+// shared by all channels), the channel's own inputs of the group are prefetched into registers.  State layout
+// in the slot: [N][inner].
 // ------------------------------------------------------------------------------------------------
-constexpr int SCAN_G = 8;
+constexpr int SCAN_G = 8, SCAN_CH = 32;  // tokens staged per barrier pair; channels per CTA (8 per warp)
 // exp of a decay exponent: correctly rounded (through fp64) in the fp32 model, where a thousand decays of one
 // state entry multiply up; the fast fp32 exponential in the bf16 model
 template <typename T> __device__ __forceinline__ float decay_of(float x);
 template <> __device__ __forceinline__ float decay_of<float>(float x) { return (float)exp((double)x); }
 template <> __device__ __forceinline__ float decay_of<bf16>(float x) { return expf(x); }
-template <typename T, int NT>
+template <typename T, int NT, int LPC>
 __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict__ x, const float* __restrict__ dt_raw,
                                                              const float* __restrict__ dt_bias,
                                                              const T* __restrict__ bc, int ld_bc, int b_off,
@@ -888,18 +891,24 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
                                                              long long slot_stride,
                                                              const int32_t* __restrict__ seq_desc, int inner, int N,
                                                              T* __restrict__ out) {
+  // LPC lanes share a channel: 4 in steps that hold prompt portions (few sequences, long chains), 1 in steps
+  // of single tokens (the state traffic is what counts there, and whole-warp rows of it are read at once)
+  constexpr int NL = NT / LPC;   // states per lane
   extern __shared__ float sm[];  // [G][2N]
   const SeqView s = seq_view(seq_desc, blockIdx.x);
-  const int c = blockIdx.y * 128 + threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = LPC == 4 ? lane >> 3 : 0;
+  const int c = LPC == 4 ? blockIdx.y * SCAN_CH + warp * 8 + (lane & 7) : blockIdx.y * 128 + (int)threadIdx.x;
+  const int n0 = sub * NL;
   const bool on = c < inner;
   float* st = state + (long long)s.slot * slot_stride;
-  float S[NT], A[NT];
+  float S[NL], A[NL];
 #pragma unroll
-  for (int n = 0; n < NT; ++n) {
+  for (int i = 0; i < NL; ++i) {
+    const int n = n0 + i;
     const bool in = on && n < N;
-    S[n] = (in && s.pos0 > 0) ? st[(long long)n * inner + c] : 0.f;
+    S[i] = (in && s.pos0 > 0) ? st[(long long)n * inner + c] : 0.f;
     // a rate is used at every token: its error would add up over a sequence, so it is rounded once, from fp64
-    A[n] = in ? -(float)exp((double)a_log[(long long)c * N + n]) : 0.f;
+    A[i] = in ? -(float)exp((double)a_log[(long long)c * N + n]) : 0.f;
   }
   const float dc = on ? dvec[c] : 0.f, dtb = (on && dt_bias) ? dt_bias[c] : 0.f;
   for (int g0 = 0; g0 < s.n; g0 += SCAN_G) {
@@ -920,30 +929,33 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const T* __restrict
       sm[e] = ldf(bc + (long long)(s.row0 + g0 + tk) * ld_bc + b_off + i);
     }
     __syncthreads();
-    if (!on) continue;
 #pragma unroll
     for (int tk = 0; tk < SCAN_G; ++tk) {
       if (tk < cnt) {
         const long long r = s.row0 + g0 + tk;
-        const float* Bv = sm + tk * 2 * N;
+        const float* Bv = sm + tk * 2 * N + n0;
         const float* Cv = Bv + N;
         const float dt = softplusf_(dtv[tk] + dtb), xv = xs[tk], dx = dt * xv;
         float y = 0.f;
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
-          if (n < N) {
-            S[n] = fmaf(decay_of<T>(dt * A[n]), S[n], dx * Bv[n]);
-            y = fmaf(S[n], Cv[n], y);
+        for (int i = 0; i < NL; ++i)
+          if (n0 + i < N) {
+            S[i] = fmaf(decay_of<T>(dt * A[i]), S[i], dx * Bv[i]);
+            y = fmaf(S[i], Cv[i], y);
           }
+        if constexpr (LPC == 4) {  // the channel's sum over its four lanes
+          y += __shfl_xor_sync(0xffffffffu, y, 8);
+          y += __shfl_xor_sync(0xffffffffu, y, 16);
+        }
         y = fmaf(dc, xv, y);
-        stf(out + r * inner + c, y * siluf_(zs[tk]));
+        if (on && sub == 0) stf(out + r * inner + c, y * siluf_(zs[tk]));
       }
     }
   }
   if (on) {
 #pragma unroll
-    for (int n = 0; n < NT; ++n)
-      if (n < N) st[(long long)n * inner + c] = S[n];
+    for (int i = 0; i < NL; ++i)
+      if (n0 + i < N) st[(long long)(n0 + i) * inner + c] = S[i];
   }
 }
 
@@ -1227,28 +1239,35 @@ int b200q_chunk_attn_seq(const float* qs, const void* cache, const int32_t* bloc
 int b200q_selective_scan(const void* x, const float* dt_raw, const float* dt_bias, const void* bc, int ld_bc, int b_off,
                          const void* z,
                          int ld_z, const float* a_log, const float* d, float* state, long long slot_stride,
-                         const int32_t* seq_desc, int n_seqs, int inner, int N, void* out, int dtype, void* stream) {
+                         const int32_t* seq_desc, int n_seqs, int inner, int N, void* out, int T_, int dtype,
+                         void* stream) {
   B200Q_CHECK_ARG(x && dt_raw && bc && z && a_log && d && state && seq_desc && out && inner > 0 && N > 0 && N <= 256 &&
                       b_off >= 0 && ld_bc >= b_off + 2 * N && ld_z >= inner && n_seqs >= 0 && is_dtype(dtype),
                   "selective_scan: bad argument (inner=%d state=%d (<= 256))", inner, N);
   if (n_seqs == 0) return B200Q_OK;
-  dim3 grid(n_seqs, (inner + 127) / 128);
+  const bool split = T_ > n_seqs;  // a step with prompt portions: four lanes per channel
+  dim3 grid(n_seqs, split ? (inner + SCAN_CH - 1) / SCAN_CH : (inner + 127) / 128);
+  B200Q_CHECK_ARG(grid.y <= 65535, "selective_scan: too many channels (%d)", inner);
   const size_t smem = (size_t)SCAN_G * 2 * N * sizeof(float);
-#define SCAN(TT, NT)                                                                                              \
-  selective_scan_kernel<TT, NT><<<grid, 128, smem, as_stream(stream)>>>(                                          \
-      (const TT*)x, dt_raw, dt_bias, (const TT*)bc, ld_bc, b_off, (const TT*)z, ld_z, a_log, d, state, slot_stride,  \
-      seq_desc,                                                                                                     \
-      inner, N, (TT*)out)
-#define SCAN_BY_N(TT)                 \
-  do {                                \
-    if (N <= 16) SCAN(TT, 16);        \
-    else if (N <= 32) SCAN(TT, 32);   \
-    else if (N <= 64) SCAN(TT, 64);   \
-    else if (N <= 128) SCAN(TT, 128); \
-    else SCAN(TT, 256);               \
+#define SCAN(TT, NT, LPC)                                                                                         \
+  selective_scan_kernel<TT, NT, LPC><<<grid, 128, smem, as_stream(stream)>>>(                                     \
+      (const TT*)x, dt_raw, dt_bias, (const TT*)bc, ld_bc, b_off, (const TT*)z, ld_z, a_log, d, state, slot_stride, \
+      seq_desc, inner, N, (TT*)out)
+#define SCAN_BY_N(TT, LPC)                 \
+  do {                                     \
+    if (N <= 16) SCAN(TT, 16, LPC);        \
+    else if (N <= 32) SCAN(TT, 32, LPC);   \
+    else if (N <= 64) SCAN(TT, 64, LPC);   \
+    else if (N <= 128) SCAN(TT, 128, LPC); \
+    else SCAN(TT, 256, LPC);               \
   } while (0)
-  if (dtype == B200Q_DTYPE_F32) SCAN_BY_N(float);
-  else SCAN_BY_N(bf16);
+  if (dtype == B200Q_DTYPE_F32) {
+    if (split) SCAN_BY_N(float, 4);
+    else SCAN_BY_N(float, 1);
+  } else {
+    if (split) SCAN_BY_N(bf16, 4);
+    else SCAN_BY_N(bf16, 1);
+  }
 #undef SCAN_BY_N
 #undef SCAN
   B200Q_LAUNCH_CHECK();

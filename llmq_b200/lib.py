@@ -210,7 +210,8 @@ SIGNATURES = {
                               _vp]),
     "b200q_chunk_attn_seq": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp, _vp, _i, _f,
                                   _vp, _i, _vp]),
-    "b200q_selective_scan": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "b200q_selective_scan": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _vp, _i, _i,
+                                  _vp]),
     "b200q_scatter_scaled_rows": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
     "b200q_silu_glu": (_i, [_vp, _vp, _i64, _i, _i, _vp]),
     "b200q_layer_sum": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp]),
