@@ -302,7 +302,7 @@ def _cycle(width: int, vocab: int, n_layers: int, heads: int, kv_heads: int, dim
             layers.append(NoridraLayer(mixer="delta", heads=heads, kv_heads=heads, dim=dim, vdim=dim, conv=4, **moe))
         elif kind == "attention":
             layers.append(NoridraLayer(mixer="attention", heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim,
-                                       scale=dim ** -0.5, softcap=30.0, chunk=2048, **moe))
+                                       scale=dim ** -0.5, softcap=50.0, chunk=2048, **moe))
         else:
             layers.append(NoridraLayer(mixer="mamba1", inner=2 * width, state=16, dt_rank=width // 16, conv=4, **moe))
     return NoridraSpec(width=width, vocab=vocab, layers=layers, rms_eps=1e-6, norm_groups=4, alpha=2.0, canon_taps=4,

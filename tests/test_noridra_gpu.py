@@ -433,7 +433,7 @@ def test_other_sizes_power_of_two_everything(cuda):
     layers = [delta(heads=4, kv_heads=4, dim=64, vdim=64, conv=4, ff="moe", ff_dim=128, n_experts=8, top_k=2),
               attn(heads=4, kv_heads=1, dim=64, chunk=64, ff="moe", ff_dim=64, n_experts=4, top_k=4),
               scan(inner=256, state=16, dt_rank=8, conv=4, ff="moe", ff_dim=128, n_experts=8, top_k=1)]
-    spec = small_spec(width=128, vocab=256, layers=layers, groups=2, taps=4, alpha=2.5)
+    spec = small_spec(width=128, vocab=256, layers=layers, groups=4, taps=2, alpha=2.0)
     sd = checkpoint(spec, seed=5)
     toks = tokens(150, spec.vocab, 8)
     want = oracle_logits(spec, sd, toks)
