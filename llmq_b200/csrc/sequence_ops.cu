@@ -1066,7 +1066,8 @@ int b200q_causal_conv(const void* in, int ld_in, int in_f32, const float* w, con
                       int act, int add_input, float* state, long long slot_stride, const int32_t* seq_desc,
                       const int32_t* row_seq, int n_seqs, void* out, int ld_out, int out_f32, int T_, int dtype,
                       void* stream) {
-  B200Q_CHECK_ARG(in && w && state && seq_desc && row_seq && out && C > 0 && taps >= 1 && taps <= CONV_MAX_TAPS &&
+  B200Q_CHECK_ARG(in && w && (state || taps == 1) && seq_desc && row_seq && out && C > 0 && taps >= 1 &&
+                      taps <= CONV_MAX_TAPS &&
                       ld_in >= C && ld_out >= C && n_seqs >= 0 && T_ >= 0 && is_dtype(dtype) && (act == 0 || act == 1),
                   "causal_conv: bad argument (C=%d taps=%d, at most %d taps)", C, taps, CONV_MAX_TAPS);
   if (T_ == 0 || n_seqs == 0) return B200Q_OK;

@@ -61,6 +61,7 @@ ONE_LAYER = {
     "gated_delta_equal_heads_wide": [delta(heads=3, kv_heads=3, dim=72, vdim=40, conv=4)],
     "gated_delta_one_tap": [delta(heads=2, kv_heads=1, dim=8, vdim=33, conv=1)],
     "chunk_attention": [attn()],
+    "chunk_attention_no_state_at_all": [attn(heads=4, kv_heads=4, dim=16, chunk=11)],   # one-tap input convolutions
     "chunk_attention_many_heads_per_key": [attn(heads=18, kv_heads=2, dim=8, chunk=7)],
     "chunk_attention_plain_causal": [attn(heads=2, kv_heads=1, dim=72, softcap=0.0, chunk=0)],
     "selective_scan": [scan()],
@@ -75,7 +76,7 @@ ONE_LAYER = {
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_mechanism_alone(cuda, name, dtype):
     spec = small_spec(width=80, vocab=97, layers=ONE_LAYER[name], groups=5 if "experts" in name else 1,
-                      taps=1 if name == "gated_delta" else 4)
+                      taps=1 if name in ("gated_delta", "chunk_attention_no_state_at_all") else 4)
     sd = checkpoint(spec, seed=11)
     toks = tokens(45, spec.vocab, 5)
     model, eng = build(spec, sd, dtype)
