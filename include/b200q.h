@@ -285,7 +285,7 @@ int b200q_moe_route_ex(const float* logits_dev, int T, int E, int top, int score
                        float* wts_dev, int32_t* group_off_dev, int32_t* perm_tok_dev, int32_t* pair_pos_dev,
                        int32_t* tile_tab_dev, int32_t* n_tiles_dev, void* stream);
 
-/* ---- post-norm layers, carried convolutions, and mixers 3-5 (sequence_ops.cu) ------------------------------
+/* ---- post-norm layers, carried convolutions, and mixers 3-5 (sequence_ops.cu, chunk_attn.cu) ------------------------------
  * seq_desc / row_seq as in b200q_batch.  `state` arguments point at the op's own region inside slot 0 of the
  * fp32 state pool; slot s is `slot_stride` floats further.  A sequence whose portion starts at position 0
  * starts from zeros whatever its slot holds. */
